@@ -307,7 +307,7 @@ int nvc_gather_rows(nvc_ctx* ctx, const nvc_bf16* x, const float* residual, cons
 /* ---- mechanisms of the models with an fp32 residual stream (Karuzen).  `dtype` arguments are NVC_DT_BF16 (serving:
  * bf16 storage, fp32 arithmetic) or NVC_DT_F32 (exact mode: fp32 storage, plain IEEE products and sums); strides are in
  * elements; buffers may be wider than the logical row (padding columns are never written). ---- */
-enum { NVC_ACT_NONE = 0, NVC_ACT_RELU2 = 1, NVC_ACT_GELU_TANH_MUL = 2 };
+enum { NVC_ACT_NONE = 0, NVC_ACT_RELU2 = 1, NVC_ACT_GELU_TANH_MUL = 2 };   /* 3, 4: NVC_ACT_GELU_TANH, NVC_ACT_GLU_CLAMP below */
 
 /* out[n, :H] = f32(table[ids[n], :H]). */
 int nvc_embed_gather_f32(nvc_ctx* ctx, const int32_t* ids, const void* table, int table_dtype, int ldt, float* out, int ldo,
@@ -449,6 +449,79 @@ int nvc_attn_paged_wide(nvc_ctx* ctx, const void* q, int ldq, const void* k_cach
 int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, float* o, int ldo,
                        float* state, const int32_t* state_slots, const int32_t* cu_seqlens, const int32_t* positions,
                        const float* decay, int B, int max_qlen, int heads, int dim, int vdim, void* stream);
+
+/* ---- mechanisms of the models with sandwich norms, rotary latent attention, the gated delta rule and softmax-routed experts
+ * (Fefozen) ---- */
+/* Norms in front of and behind a sublayer on an fp32 residual stream, in one pass over the row (all sums fp32):
+ *   s = res_in[r] + y[r] / sqrt(mean(y[r]^2) + eps) * (wy + weight_offset)      (y == NULL: s = res_in[r]);
+ *   res_out[r] = s (optional, may alias res_in);   out[i, :H] = s / sqrt(mean(s^2) + eps) * (w + weight_offset)   (w == NULL: none).
+ * y is the sublayer's output (fp32 [*, ld]), wy the weight of the norm behind it, w the weight of the norm in front of the next
+ * sublayer; weight_offset = 1 for weights stored around zero.  rows as in nvc_rms_norm_pair (gathers; res_out must be NULL). */
+int nvc_rms_norm_sandwich(nvc_ctx* ctx, const float* res_in, const float* y, const float* wy, float* res_out, int ld, const float* w,
+                          void* out, int out_dtype, int ldo, float eps, float weight_offset, const int32_t* rows, int N, int H,
+                          void* stream);
+/* nvc_latent_norm_store for latent attention with a rotated key part that all heads share: the cache row of a token is
+ *   [ rmsnorm(in[n, off1 : off1 + n1]) * w1 | rot(in[n, off1 + n1 : off1 + n1 + rot_dim]) ]
+ * where rot turns the first rot_dims numbers of the part by the angles of positions[n] ((cos, sin) table of
+ * nvc_rotary_table_init_sync; pairs (2i, 2i + 1), or (i, i + rot_dims / 2) when rot_half) and leaves the rest.  cache == NULL:
+ * only the query latent (a layer that reads another layer's rows). */
+int nvc_latent_norm_store_rot(nvc_ctx* ctx, const float* in, int ldi, int n0, int off1, int n1, const float* w0, const float* w1,
+                              float eps, void* out0, int ld0, void* cache, int ldc, const int32_t* slot_mapping, int rot_dim,
+                              int rot_dims, int rot_half, const float* rot_table, const int32_t* positions, int dtype, int N,
+                              void* stream);
+/* Heads of a query projection laid out [heads][dim | rot_dim] (fp32 rows `in`): the unrotated part of head h goes to
+ * out_a[n, h * hs_a : + dim], the rotated part (first rot_dims numbers turned as above) to out_b[n, h * hs_b + off_b : + rot_dim]. */
+int nvc_head_split_rot(nvc_ctx* ctx, const float* in, int ldi, int heads, int dim, int rot_dim, int rot_dims, int rot_half,
+                       const float* rot_table, const int32_t* positions, void* out_a, int ld_a, int hs_a, void* out_b, int ld_b,
+                       int hs_b, int off_b, int dtype, int N, void* stream);
+/* nvc_head_gate with a weight of vdim numbers shared by the heads on the normed output (NULL: none). */
+int nvc_head_gate_w(nvc_ctx* ctx, const float* o, int ldo, const float* gate, int ldg, const float* weight, void* out, int ldout,
+                    int out_dtype, int heads, int vdim, int norm, float eps, int act, float out_scale, int N, void* stream);
+/* nvc_act_mul with parameters.  NVC_ACT_GELU_TANH: out = gelu_tanh(in[n, j]).  NVC_ACT_GLU_CLAMP: g = min(in[n, j], p0),
+ * u = clamp(in[n, Fp + j], -p0, p0), out = g * sigmoid(p1 * g) * (u + 1). */
+enum { NVC_ACT_GELU_TANH = 3, NVC_ACT_GLU_CLAMP = 4 };
+int nvc_act_mul_p(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int dtype, int N, int F, int Fp, int kind, float p0, float p1,
+                  void* stream);
+/* nvc_moe_route_logits with a choice of score function and weights: score NVC_ROUTE_SIGMOID or NVC_ROUTE_SOFTMAX (over all E
+ * columns); normalize != 0: topk_w = s_chosen / (sum of the chosen s + 1e-20) * scale, else topk_w = s_chosen * scale. */
+enum { NVC_ROUTE_SIGMOID = 0, NVC_ROUTE_SOFTMAX = 1 };
+int nvc_moe_route_logits_ex(nvc_ctx* ctx, const float* z, int ldz, const float* correction, int E, int top, float scale, int gate_col,
+                            int score, int normalize, int32_t* topk_idx, float* topk_w, float* gate, int N, void* stream);
+/* nvc_moe_sort_padded for a router whose experts from E_real on have no product (identity experts): their tiles get
+ * tile_group -1. */
+int nvc_moe_sort_padded_ex(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int E_real, int align, int32_t* offsets,
+                           int32_t* src_rows, int32_t* pos, int32_t* tile_group, int tiles_cap, void* stream);
+/* nvc_moe_combine where the experts from E_real on are identity experts: a pair (n, t) with topk_idx[n, t] >= E_real contributes
+ * topk_w[n, t] * x[n, :H] instead of a row of y. */
+int nvc_moe_combine_identity(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int32_t* pos, const float* topk_w,
+                             const int32_t* topk_idx, int top, int E_real, const void* x, int x_dtype, int ldx, float* out, int ldo,
+                             int N, int H, void* stream);
+/* Gated delta rule, the part between the fused projection and the recurrence, over the new tokens of every sequence:
+ *   q, k, v channels: causal convolution over time per channel (conv_w [C, taps], last column = the current token; the taps - 1
+ *   inputs in front of a portion come from conv_state [slots, taps - 1, C], zeros when the portion starts at position 0), silu;
+ *   q and k heads: x / sqrt(sum(x^2) + unit_eps), q times q_scale;   beta = sigmoid(in[b_off + h]);
+ *   decay = exp(-exp(A_log[h]) * softplus(in[a_off + h] + dt_bias[h])).
+ * Channel order of conv_w and conv_state: q (kv_heads * dim), k (kv_heads * dim), v (heads * vdim).  Outputs are fp32 rows;
+ * gb_out [N, 2 * heads] = (decay, beta) per head.  The conv state is NOT advanced here (nvc_delta_rule_scan does it). */
+typedef struct nvc_delta_prep {
+  const float* in; int ldi;
+  int q_off, k_off, v_off, b_off, a_off;
+  int heads, kv_heads, dim, vdim, taps;
+  const float* conv_w;
+  float* conv_state;
+  const int32_t* state_slots; const int32_t* cu_seqlens; const int32_t* positions;
+  const float* A_log; const float* dt_bias;
+  float unit_eps, q_scale;
+  float* q_out; float* k_out; float* v_out; int ldq, ldk, ldv;
+  float* gb_out;
+  int B;
+} nvc_delta_prep;
+int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, void* stream);
+/* The recurrence, per (sequence, head) with state S [dim, vdim] fp32 in state [slots, heads, dim, vdim]:
+ *   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q        (head h reads q / k head h / (heads / kv_heads))
+ * token by token over rows cu_seqlens[b] .. cu_seqlens[b + 1] (row b when cu_seqlens == NULL); a sequence starts from zeros when
+ * positions[first row] == 0.  Also advances the convolution state of nvc_delta_prep_run (p->in still holds the step's rows). */
+int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float* o, int ldo, float* state, int max_qlen, void* stream);
 
 /* K8. Replaces Qwen3ModelRunner::argmax (src/engine/llm_engine.rs:135-142) on device:
  * idx[b] = LAST index of the maximum of logits[b, :] (Iterator::max_by tie rule);

@@ -12,7 +12,11 @@
 // weight rows, its "W" rows are tokens - and the epilogue stores its accumulator row r as COLUMN r of C: lm_head at decode
 // batch sizes, where 64 tokens would fill a quarter of a 256-row MMA and only one CTA of the pair would hold valid rows.
 // NVC_EPI_RELU2: C = max(acc, 0)^2, element by element (the experts of the Karuzen family), any output type.
-enum { NVC_EPI_NONE = 0, NVC_EPI_SILU_MUL = 1, NVC_EPI_TRANSPOSE = 2, NVC_EPI_QK_NORM_ROPE = 3, NVC_EPI_GELU_TANH_MUL = 4, NVC_EPI_RELU2 = 5 };
+// NVC_EPI_GELU_TANH: C = gelu_tanh(acc), element by element (a plain, ungated feed-forward), any output type.
+enum { NVC_EPI_NONE = 0, NVC_EPI_SILU_MUL = 1, NVC_EPI_TRANSPOSE = 2, NVC_EPI_QK_NORM_ROPE = 3, NVC_EPI_GELU_TANH_MUL = 4, NVC_EPI_RELU2 = 5,
+       NVC_EPI_GELU_TANH = 6 };
+// the element-wise epilogues
+__host__ __device__ __forceinline__ bool nvc_epi_unary(int epi) { return epi == NVC_EPI_RELU2 || epi == NVC_EPI_GELU_TANH; }
 
 // the gated epilogues write half as many columns as the accumulator has
 __host__ __device__ __forceinline__ bool nvc_epi_gated(int epi) { return epi == NVC_EPI_SILU_MUL || epi == NVC_EPI_GELU_TANH_MUL; }
@@ -34,12 +38,22 @@ __device__ __forceinline__ void nvc_gated16(int epi, const float* f, float* o) {
     }
   }
 }
-// squared relu of 32 accumulator columns
-__device__ __forceinline__ void nvc_relu2_32(const float* f, float* o) {
+// squared relu or tanh-gelu (hardware tanh) of 32 accumulator columns
+__device__ __forceinline__ void nvc_unary32(int epi, const float* f, float* o) {
+  if (epi == NVC_EPI_RELU2) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    const float r = fmaxf(f[j], 0.f);
-    o[j] = r * r;
+    for (int j = 0; j < 32; ++j) {
+      const float r = fmaxf(f[j], 0.f);
+      o[j] = r * r;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float z = f[j];
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+      o[j] = 0.5f * z * (1.0f + t);
+    }
   }
 }
 #endif
@@ -75,7 +89,7 @@ __device__ __forceinline__ void store16(void* C, int out_f32, int64_t off, const
 //                    rows [16g,16g+16)), so f[0..16) = gate and f[16..32) = up of features n0/2 .. n0/2+16:
 //                    C[row, n0/2 .. n0/2+16) = silu(gate) * up   (src/layers/activation.rs:13-18,
 //                    silu(x) = x / (1 + exp(-x)) in f32), bf16.  row_off = row * ldc in elements of C.
-// kUnary = false compiles the element-wise epilogues (NVC_EPI_RELU2) out: the decode GEMMs of the dense models keep their code.
+// kUnary = false compiles the element-wise epilogues (NVC_EPI_RELU2, NVC_EPI_GELU_TANH) out: the decode GEMMs of the dense models keep their code.
 template <bool kUnary = true>
 __device__ __forceinline__ void emit32(void* C, int out_f32, int epi, int64_t row_off, int n0, int N, const float* f) {
   if (nvc_epi_gated(epi)) {
@@ -87,9 +101,9 @@ __device__ __forceinline__ void emit32(void* C, int out_f32, int epi, int64_t ro
       store16(C, 0, row_off + (n0 >> 1), o);
     }
   } else {
-    if (kUnary && epi == NVC_EPI_RELU2) {          // a branch of its own, uniform over the grid
+    if (kUnary && nvc_epi_unary(epi)) {          // a branch of its own, uniform over the grid
       float g[32];
-      nvc_relu2_32(f, g);
+      nvc_unary32(epi, f, g);
       if (n0 < N) store16(C, out_f32, row_off + n0, g);
       if (n0 + 16 < N) store16(C, out_f32, row_off + n0 + 16, g + 16);
       return;
@@ -146,9 +160,9 @@ struct RowStage {
       if (filled == 128) flush(lane);
       return;
     }
-    if (epi == NVC_EPI_RELU2) {          // a branch of its own (uniform over the grid): the plain path pays nothing for it
+    if (nvc_epi_unary(epi)) {          // a branch of its own (uniform over the grid): the plain path pays nothing for it
       float g[32];
-      nvc_relu2_32(f, g);
+      nvc_unary32(epi, f, g);
       put32(lane, out_f32, g);
     } else {
       put32(lane, out_f32, f);

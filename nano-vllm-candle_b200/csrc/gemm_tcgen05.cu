@@ -437,7 +437,7 @@ int launch(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C,
   NVC_REQUIRE(ctx, !ks || (size_t)BN * BM * 4 <= (size_t)cfg::kStages * cfg::kStageBytes, NVC_EINVAL, "ring too small for the partial tile");
   // the extended variant exists for CL = 1 (the grouped products and the element-wise epilogues never use clusters)
   constexpr bool kHasExt = CL == 1;
-  const bool ext = tile_group != nullptr || epi == NVC_EPI_RELU2;
+  const bool ext = tile_group != nullptr || nvc_epi_unary(epi);
   NVC_REQUIRE(ctx, !ext || kHasExt, NVC_EINVAL, "grouped / element-wise epilogue products need a cluster size of 1");
   auto kernel = gemm_bf16_tcgen05_kernel<BN, KPS, CL, false>;
   if constexpr (kHasExt) { if (ext) kernel = gemm_bf16_tcgen05_kernel<BN, KPS, CL, true>; }
@@ -553,7 +553,7 @@ static int gemm_impl(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W
   NVC_REQUIRE(ctx, lda % 8 == 0 && lda >= K, NVC_ESHAPE, "lda must be >= K and a multiple of 8");
   NVC_REQUIRE(ctx, ldc >= (nvc_epi_gated(epi) ? Nout / 2 : Nout) && ldc % 8 == 0, NVC_ESHAPE,
               "ldc must be >= the output width and a multiple of 8");
-  NVC_REQUIRE(ctx, epi == NVC_EPI_NONE || epi == NVC_EPI_RELU2 || (nvc_epi_gated(epi) && Nout % 32 == 0 && out_dtype == NVC_DT_BF16),
+  NVC_REQUIRE(ctx, epi == NVC_EPI_NONE || nvc_epi_unary(epi) || (nvc_epi_gated(epi) && Nout % 32 == 0 && out_dtype == NVC_DT_BF16),
               NVC_ESHAPE, "fused SiLU-mul epilogue needs Nout % 32 == 0 and bf16 output");
   NVC_REQUIRE(ctx, out_dtype == NVC_DT_BF16 || out_dtype == NVC_DT_F32, NVC_EINVAL, "bad out_dtype");
   NVC_REQUIRE(ctx, ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)C % 16) == 0, NVC_EINVAL,
@@ -599,7 +599,7 @@ static int gemm_impl(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W
     splits = 1;
     ks = 0;
     if (bn < 32) { bn = 32; kps = 4; cl = 1; }
-    if (epi == NVC_EPI_RELU2) cl = 1;          // (every (bn, kps) the choice returns has a CL = 1 instantiation)
+    if (nvc_epi_unary(epi)) cl = 1;          // (every (bn, kps) the choice returns has a CL = 1 instantiation)
   }
   if (splits > K / BK) splits = K / BK;
   const int tiles = ((M + BM - 1) / BM) * ((Nout + bn - 1) / bn);
@@ -654,8 +654,10 @@ extern "C" int nvc_gemm_bf16_gelu_mul(nvc_ctx* ctx, const nvc_bf16* A, int lda, 
 // C = act(A W^T) with the plain activations of nvc_linear (NVC_ACT_NONE, NVC_ACT_RELU2) in the epilogue.
 extern "C" int nvc_gemm_bf16_act(nvc_ctx* ctx, const nvc_bf16* A, int lda, const nvc_bf16* W, void* C, int ldc, int out_dtype, int M,
                                  int Nout, int K, int act, void* stream) {
-  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2, NVC_EINVAL, "activation must be NVC_ACT_NONE or NVC_ACT_RELU2");
-  return gemm_impl(ctx, A, lda, W, C, ldc, out_dtype, M, Nout, K, 0, 0, act == NVC_ACT_RELU2 ? NVC_EPI_RELU2 : NVC_EPI_NONE, stream, nullptr);
+  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2 || act == NVC_ACT_GELU_TANH, NVC_EINVAL,
+              "activation must be NVC_ACT_NONE, NVC_ACT_RELU2 or NVC_ACT_GELU_TANH");
+  const int epi = act == NVC_ACT_RELU2 ? NVC_EPI_RELU2 : (act == NVC_ACT_GELU_TANH ? NVC_EPI_GELU_TANH : NVC_EPI_NONE);
+  return gemm_impl(ctx, A, lda, W, C, ldc, out_dtype, M, Nout, K, 0, 0, epi, stream, nullptr);
 }
 
 // Grouped product on the 1-CTA kernel: rows of A sorted by group with every group starting at a multiple of 128 rows

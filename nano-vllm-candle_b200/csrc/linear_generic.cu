@@ -86,6 +86,7 @@ linear_kernel(const T* __restrict__ A, int lda, int64_t sa, const int32_t* __res
       if (c >= N) continue;
       float v = acc[i][j];
       if (act == NVC_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+      else if (act == NVC_ACT_GELU_TANH) v = gelu_tanh_f32(v);
       st_f(C + (int64_t)r * ldc + c, v);
     }
   }
@@ -207,6 +208,7 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int64_t sa, cons
         const int c = col0 + wn + nt * 8 + 2 * tq;
         float v0 = acc[mt][nt][2 * hf], v1 = acc[mt][nt][2 * hf + 1];
         if (act == NVC_ACT_RELU2) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
+        else if (act == NVC_ACT_GELU_TANH) { v0 = gelu_tanh_f32(v0); v1 = gelu_tanh_f32(v1); }
         TC* dst = C + (int64_t)r * ldc + c;
         if (c + 1 < N && (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(TC))) == 0) {     // the pair in one store
           if constexpr (sizeof(TC) == 2) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
@@ -284,7 +286,7 @@ int nvc_linear(nvc_ctx* ctx, const void* A, int lda, int64_t sa, const void* W, 
                int in_dtype, int out_dtype, int M, int N, int K, int batch, int act, void* stream) {
   NVC_REQUIRE(ctx, ctx && A && W && C, NVC_EINVAL, "null pointer");
   NVC_REQUIRE(ctx, M >= 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535 && lda >= K && ldw >= K && ldc >= N, NVC_EINVAL, "bad sizes");
-  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2, NVC_EINVAL, "bad activation");
+  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2 || act == NVC_ACT_GELU_TANH, NVC_EINVAL, "bad activation");
   if (M == 0) return NVC_OK;
   return dispatch(ctx, dim3((M + TM - 1) / TM, (N + TN - 1) / TN, batch), stream, in_dtype, out_dtype, A, lda, sa, nullptr, W, ldw, sw,
                   C, ldc, sc, nullptr, 0, M, N, K, act);
@@ -295,7 +297,7 @@ int nvc_linear_grouped(nvc_ctx* ctx, const void* A, int lda, const int32_t* a_ro
                        void* stream) {
   NVC_REQUIRE(ctx, ctx && A && W && C && offsets, NVC_EINVAL, "null pointer");
   NVC_REQUIRE(ctx, max_rows >= 0 && groups > 0 && N > 0 && K > 0 && lda >= K && ldw >= K && ldc >= N, NVC_EINVAL, "bad sizes");
-  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2, NVC_EINVAL, "bad activation");
+  NVC_REQUIRE(ctx, act == NVC_ACT_NONE || act == NVC_ACT_RELU2 || act == NVC_ACT_GELU_TANH, NVC_EINVAL, "bad activation");
   if (max_rows == 0) return NVC_OK;
   // every group may end with a partial tile: at most max_rows / TM + groups tiles exist
   const int tiles = max_rows / TM + groups;

@@ -188,6 +188,82 @@ int parse_ranilix(const JValue& root, nvc_ranilix_config& c) {
   return NVC_OK;
 }
 
+
+int parse_fefozen(const JValue& root, nvc_fefozen_config& c) {
+  std::string err;
+  if (!get_int(&root, "vocab", c.vocab, 1, err) || !get_int(&root, "width", c.width, 1, err)) return cfg_fail(err);
+  const JValue* norm = root.get("norm");
+  if (!norm || norm->kind != JValue::Obj || !get_float(norm, "eps", c.eps, err)) return cfg_fail("norm.eps: " + err);
+  const JValue* layers = root.get("layers");
+  if (!layers || layers->kind != JValue::Arr || layers->arr.empty()) return cfg_fail("`layers` must be a non-empty list");
+  for (size_t i = 0; i < layers->arr.size(); ++i) {
+    const JValue& jl = layers->arr[i];
+    const std::string where = "layers[" + std::to_string(i) + "]: ";
+    if (jl.kind != JValue::Obj) return cfg_fail(where + "not an object");
+    nvc_fefozen_layer L;
+    const JValue* type = jl.get("type");
+    const JValue* m = jl.get("mixer");
+    if (!type || type->kind != JValue::Str) return cfg_fail(where + "missing `type`");
+    if (!m || m->kind != JValue::Obj) return cfg_fail(where + "missing `mixer`");
+    if (type->str == "latent_attention" || type->str == "latent_attention_2") {
+      L.kind = nvc_fefozen_layer::Latent;
+      auto& a = L.lat;
+      a.rot_half = type->str == "latent_attention_2";
+      a.sink = !a.rot_half;
+      if (!get_int(m, "heads", a.heads, 1, err) || !get_int(m, "dim", a.dim, 1, err) || !get_int(m, "rot_dim", a.rot_dim, 0, err) ||
+          !get_int(m, "vdim", a.vdim, 1, err) || !get_int(m, "kv_rank", a.kv_rank, 1, err) || !get_int(m, "q_rank", a.q_rank, 1, err) ||
+          !get_float(m, "scale", a.scale, err) || !parse_rotary(m, a.rot, a.rot_dim, err))
+        return cfg_fail(where + "mixer: " + err);
+      const JValue* from = m->get("kv_from");
+      if (from && from->kind != JValue::Null) {
+        if (!get_int(m, "kv_from", a.kv_from, 0, err)) return cfg_fail(where + "mixer: " + err);
+        if (a.kv_from >= (int)i) return cfg_fail(where + "mixer.kv_from must name an earlier layer");
+        const auto& src = c.layers[a.kv_from];
+        if (src.kind != nvc_fefozen_layer::Latent || src.lat.kv_from >= 0) return cfg_fail(where + "mixer.kv_from must name a latent-attention layer with a cache of its own");
+        if (src.lat.kv_rank != a.kv_rank || src.lat.rot_dim != a.rot_dim || src.lat.rot.dims != a.rot.dims || src.lat.rot.base != a.rot.base ||
+            src.lat.rot_half != a.rot_half)
+          return cfg_fail(where + "mixer.kv_from: kv_rank, rot_dim and the rotation must equal the named layer's");
+      }
+    } else if (type->str == "delta") {
+      L.kind = nvc_fefozen_layer::Delta;
+      auto& d = L.delta;
+      if (!get_int(m, "heads", d.heads, 1, err) || !get_int(m, "kv_heads", d.kv_heads, 1, err) || !get_int(m, "dim", d.dim, 1, err) ||
+          !get_int(m, "vdim", d.vdim, 1, err) || !get_int(m, "conv", d.taps, 1, err))
+        return cfg_fail(where + "mixer: " + err);
+      if (d.heads % d.kv_heads != 0) return cfg_fail(where + "mixer: heads must be a multiple of kv_heads");
+    } else {
+      return cfg_fail(where + "mixer type `" + type->str + "` is not supported");
+    }
+    const JValue* mlp = jl.get("mlp");
+    if (mlp && mlp->kind == JValue::Obj) {
+      const JValue* kind = mlp->get("kind");
+      if (!kind || kind->kind != JValue::Str) return cfg_fail(where + "mlp: missing `kind`");
+      if (kind->str == "dense") {
+        L.mlp.kind = nvc_routed_mlp_spec::Dense;
+        if (!get_int(mlp, "ff", L.mlp.ff, 1, err)) return cfg_fail(where + "mlp: " + err);
+      } else if (kind->str == "moe") {
+        L.mlp.kind = nvc_routed_mlp_spec::Moe;
+        const JValue* r = mlp->get("router");
+        const JValue* e = mlp->get("expert");
+        if (!r || !e) return cfg_fail(where + "mlp: a mixture of experts needs `router` and `expert`");
+        if (!get_int(r, "experts", L.mlp.experts, 0, err) || !get_int(r, "top", L.mlp.top, 1, err) || !get_int(e, "ff", L.mlp.expert_ff, 1, err) ||
+            !get_float(e, "limit", L.mlp.limit, err))
+          return cfg_fail(where + "mlp: " + err);
+        if (r->get("identity") && r->get("identity")->kind != JValue::Null && !get_int(r, "identity", L.mlp.identity, 0, err))
+          return cfg_fail(where + "mlp: " + err);
+        if (L.mlp.experts + L.mlp.identity < 1 || L.mlp.top > L.mlp.experts + L.mlp.identity) return cfg_fail(where + "mlp: top exceeds the experts");
+        if (L.mlp.experts + L.mlp.identity > 256) return cfg_fail(where + "mlp: at most 256 experts, identity experts included");
+      } else {
+        return cfg_fail(where + "mlp kind `" + kind->str + "` is not supported");
+      }
+    } else if (mlp && mlp->kind != JValue::Null) {
+      return cfg_fail(where + "`mlp` must be an object or null");
+    }
+    c.layers.push_back(L);
+  }
+  return NVC_OK;
+}
+
 }  // namespace
 
 std::vector<nvc_karuzen_config::Run> nvc_karuzen_config::runs() const {
@@ -223,10 +299,12 @@ int nvc_model_config_from_json(const char* text, nvc_model_config** out) {
     rc = parse_karuzen(root, c->karuzen);
   } else if (arch == "Ranilix") {
     rc = parse_ranilix(root, c->ranilix);
+  } else if (arch == "Fefozen") {
+    rc = parse_fefozen(root, c->fefozen);
   } else if (arch == "Qwen3ForCausalLM") {
     // parsed by nvc_qwen3_config_from_hf_dir (hf_loader.cpp) when loaded from a directory
   } else {
-    rc = cfg_fail("architecture `" + arch + "` is not registered (known: Qwen3ForCausalLM, Karuzen, Ranilix)");
+    rc = cfg_fail("architecture `" + arch + "` is not registered (known: Qwen3ForCausalLM, Karuzen, Ranilix, Fefozen)");
   }
   if (rc) { delete c; return rc; }
   *out = c;
@@ -251,11 +329,12 @@ const char* nvc_model_config_architecture(const nvc_model_config* c) { return c 
 int nvc_model_config_vocab(const nvc_model_config* c) {
   if (!c) return 0;
   if (c->architecture == "Ranilix") return c->ranilix.vocab;
+  if (c->architecture == "Fefozen") return c->fefozen.vocab;
   return c->architecture == "Karuzen" ? c->karuzen.vocab : c->qwen3.vocab_size;
 }
 int nvc_model_config_layer_runs(const nvc_model_config* c, int32_t* layers, int32_t* passes, int32_t* readd, int capacity) {
-  if (c && c->architecture == "Ranilix") {      // no looped block: every layer runs once
-    const int n = (int)c->ranilix.layers.size();
+  if (c && (c->architecture == "Ranilix" || c->architecture == "Fefozen")) {      // no looped block: every layer runs once
+    const int n = (int)(c->architecture == "Ranilix" ? c->ranilix.layers.size() : c->fefozen.layers.size());
     for (int i = 0; i < n && i < capacity; ++i) {
       if (layers) layers[i] = i;
       if (passes) passes[i] = 0;

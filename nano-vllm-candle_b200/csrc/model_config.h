@@ -79,10 +79,50 @@ struct nvc_ranilix_config {
   }
 };
 
+// Fefozen: a stack of sequential layers with a norm in front of and behind each sublayer (RMS norms whose weights are stored
+// around zero), x <- x + n1b(mixer(n1(x))), x <- x + n2b(ff(n2(x))).  Mixers: latent attention with a rotated key part that all
+// heads share (a token leaves [normed latent | rotated part] in the cache; optional sink; sigmoid output gate; a layer may read
+// another layer's rows), or the gated delta rule (short convolutions, a per-head recurrent state).  Feed-forward: dense tanh-gelu
+// or softmax-routed experts with identity experts and clamped gated units.  Tied logits.
+struct nvc_latent_attn_spec {
+  int heads = 0, dim = 0, rot_dim = 0, vdim = 0, kv_rank = 0, q_rank = 0;
+  float scale = 0.f;
+  nvc_rotary_spec rot;       // on the rot_dim part of queries and of the shared key part
+  bool rot_half = false;     // pairs (i, i + dims / 2) instead of (2i, 2i + 1)
+  bool sink = false;         // one more term exp(sink_h) in the softmax denominator
+  int kv_from = -1;          // >= 0: no key / value down-projection of its own, reads that layer's cache rows
+};
+struct nvc_delta_spec {
+  int heads = 0, kv_heads = 0, dim = 0, vdim = 0, taps = 1;
+};
+struct nvc_routed_mlp_spec {
+  enum Kind { None, Dense, Moe } kind = None;
+  int ff = 0;                                       // dense
+  int experts = 0, identity = 0, top = 0, expert_ff = 0;   // moe: `identity` pass-through experts behind the real ones
+  float limit = 0.f;                                // clamp of the gated units
+};
+struct nvc_fefozen_layer {
+  enum Kind { Latent, Delta } kind = Latent;
+  nvc_latent_attn_spec lat;
+  nvc_delta_spec delta;
+  nvc_routed_mlp_spec mlp;
+};
+struct nvc_fefozen_config {
+  int vocab = 0, width = 0;
+  float eps = 1e-5f;
+  std::vector<nvc_fefozen_layer> layers;
+  bool has_state() const {
+    for (auto& l : layers)
+      if (l.kind == nvc_fefozen_layer::Delta) return true;
+    return false;
+  }
+};
+
 struct nvc_model_config {
-  std::string architecture;   // "Qwen3ForCausalLM", "Karuzen" or "Ranilix"
+  std::string architecture;   // "Qwen3ForCausalLM", "Karuzen", "Ranilix" or "Fefozen"
   nvc_qwen3_config qwen3{};
   int qwen3_tied = 0;
   nvc_karuzen_config karuzen;
   nvc_ranilix_config ranilix;
+  nvc_fefozen_config fefozen;
 };

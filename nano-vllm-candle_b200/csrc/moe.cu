@@ -13,7 +13,7 @@ constexpr int kMaxPerLane = 8;   // experts <= 256
 // top-k by repeated arg-max over the choice scores c (ties -> the lower expert index); expert e lives in lane e % 32,
 // slot e / 32.  Writes idx / weights of token n: s_chosen / (sum of the chosen s + 1e-20) * scale.
 __device__ __forceinline__ void topk_write(float (&s)[kMaxPerLane], float (&c)[kMaxPerLane], int lane, int E, int top, float scale,
-                                           int32_t* __restrict__ idx, float* __restrict__ wout, int64_t n) {
+                                           int32_t* __restrict__ idx, float* __restrict__ wout, int64_t n, bool normalize = true) {
   // top-k by repeated arg-max over the choice scores (ties -> the lower expert index)
   float sel_sum = 0.f, my_w = 0.f;
   int my_e = 0;
@@ -46,13 +46,14 @@ __device__ __forceinline__ void topk_write(float (&s)[kMaxPerLane], float (&c)[k
     }
   }
   __syncwarp();
-  const float inv = scale / (sel_sum + 1e-20f);
+  const float inv = normalize ? scale / (sel_sum + 1e-20f) : scale;
   for (int t = lane; t < top; t += 32) wout[(int64_t)n * top + t] *= inv;
 }
 
 // scores from logits that a matrix product has already taken: z [N, ldz] fp32, column gate_col (if >= 0) = the shared gate
 __global__ void moe_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int E, int top, float scale,
-                                int gate_col, int32_t* __restrict__ idx, float* __restrict__ wout, float* __restrict__ gate, int N) {
+                                int gate_col, int score, int normalize, int32_t* __restrict__ idx, float* __restrict__ wout,
+                                float* __restrict__ gate, int N) {
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -65,13 +66,31 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, int ldz, const floa
     const int e = lane + 32 * i;
     s[i] = 0.f;
     c[i] = -INFINITY;
-    if (e < E) {
-      s[i] = sigmoid_f32(zr[e]);
-      c[i] = s[i] + __ldg(corr + e);
-    }
+    if (e < E) s[i] = zr[e];
   }
+  if (score == NVC_ROUTE_SOFTMAX) {       // over all E columns, fp32
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (lane + 32 * i < E) mx = fmaxf(mx, s[i]);
+    mx = warp_max(mx);
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (lane + 32 * i < E) { s[i] = expf(s[i] - mx); den += s[i]; }
+    den = warp_sum(den);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) s[i] = s[i] / den;
+  } else {
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (lane + 32 * i < E) s[i] = sigmoid_f32(s[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i)
+    if (lane + 32 * i < E) c[i] = s[i] + __ldg(corr + lane + 32 * i);
   if (gate_col >= 0 && gate && lane == 0) gate[n] = sigmoid_f32(zr[gate_col]);
-  topk_write(s, c, lane, E, top, scale, idx, wout, n);
+  topk_write(s, c, lane, E, top, scale, idx, wout, n, normalize != 0);
 }
 
 template <typename T>
@@ -127,7 +146,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int ldh, const float* 
 // expert's group, and the warp then places its pairs in order (__match_any_sync ranks equal experts inside a batch of
 // 32).  Within an expert the pairs keep token order, so the layout - and every sum downstream - is deterministic.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int align, int32_t* __restrict__ offsets,
+moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int E_real, int align, int32_t* __restrict__ offsets,
                 int32_t* __restrict__ src_rows, int32_t* __restrict__ pos, int32_t* __restrict__ tile_group, int tiles_cap) {
   extern __shared__ int32_t sm[];   // [32][E] counts -> starts, then [E + 1] offsets, then [E] sizes
   int32_t* cnt = sm;
@@ -158,7 +177,7 @@ moe_sort_kernel(const int32_t* __restrict__ idx, int P, int top, int E, int alig
     for (int e = warp; e < E; e += blockDim.x >> 5) {
       for (int r = off[e] + size[e] + lane; r < off[e + 1]; r += 32) src_rows[r] = -1;
       if (tile_group)
-        for (int t = off[e] / align + lane; t < off[e + 1] / align; t += 32) tile_group[t] = e;
+        for (int t = off[e] / align + lane; t < off[e + 1] / align; t += 32) tile_group[t] = e < E_real ? e : -1;   // no product behind an identity expert
     }
     if (tile_group)
       for (int t = off[E] / align + threadIdx.x; t < tiles_cap; t += blockDim.x) tile_group[t] = -1;
@@ -201,6 +220,25 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ in, int ld_in, cons
     if (r >= n) break;
     const int src = src_rows[r];
     out[(int64_t)r * ld_out + c] = src >= 0 ? in[(int64_t)src * ld_in + c] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// experts from E_real on are identity experts: their pairs read the token's own row x[n] instead of a row of y
+template <typename TY, typename TX>
+__global__ void moe_combine_identity_kernel(const TY* __restrict__ y, int ldy, const int32_t* __restrict__ pos, const float* __restrict__ w,
+                                            const int32_t* __restrict__ idx, int top, int E_real, const TX* __restrict__ x, int ldx,
+                                            float* __restrict__ out, int ldo, int H) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float a = 0.f;
+    for (int t = 0; t < top; ++t) {
+      const int64_t p = (int64_t)n * top + t;
+      const float v = idx[p] < E_real ? ld_f(y + (int64_t)pos[p] * ldy + j) : ld_f(x + (int64_t)n * ldx + j);
+      a = fmaf(w[p], v, a);
+    }
+    out[(int64_t)n * ldo + j] = a;
   }
 }
 
@@ -266,12 +304,18 @@ int nvc_moe_route(nvc_ctx* ctx, const void* h, int h_dtype, int ldh, const float
 
 int nvc_moe_route_logits(nvc_ctx* ctx, const float* z, int ldz, const float* correction, int E, int top, float scale, int gate_col,
                          int32_t* topk_idx, float* topk_w, float* gate, int N, void* stream) {
+  return nvc_moe_route_logits_ex(ctx, z, ldz, correction, E, top, scale, gate_col, NVC_ROUTE_SIGMOID, 1, topk_idx, topk_w, gate, N, stream);
+}
+
+int nvc_moe_route_logits_ex(nvc_ctx* ctx, const float* z, int ldz, const float* correction, int E, int top, float scale, int gate_col,
+                            int score, int normalize, int32_t* topk_idx, float* topk_w, float* gate, int N, void* stream) {
   NVC_REQUIRE(ctx, ctx && z && correction && topk_idx && topk_w, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, score == NVC_ROUTE_SIGMOID || score == NVC_ROUTE_SOFTMAX, NVC_EINVAL, "unknown score function");
   NVC_REQUIRE(ctx, E > 0 && E <= 32 * kMaxPerLane && top > 0 && top <= E, NVC_ESHAPE, "experts must be in [1, 256], top in [1, experts]");
   NVC_REQUIRE(ctx, N >= 0 && ldz >= E && gate_col < ldz && (gate_col < 0 || gate), NVC_EINVAL, "bad sizes");
   if (N == 0) return NVC_OK;
   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_topk_kernel, dim3((N + 3) / 4), dim3(128), 0, nvc_stream(stream), z, ldz, correction, E, top, scale,
-                                 gate_col, topk_idx, topk_w, gate, N));
+                                 gate_col, score, normalize, topk_idx, topk_w, gate, N));
   ctx->launches++;
   return NVC_OK;
 }
@@ -283,12 +327,18 @@ int nvc_moe_sort(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, i
 
 int nvc_moe_sort_padded(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int align, int32_t* offsets, int32_t* src_rows,
                         int32_t* pos, int32_t* tile_group, int tiles_cap, void* stream) {
+  return nvc_moe_sort_padded_ex(ctx, topk_idx, N, top, E, E, align, offsets, src_rows, pos, tile_group, tiles_cap, stream);
+}
+
+int nvc_moe_sort_padded_ex(nvc_ctx* ctx, const int32_t* topk_idx, int N, int top, int E, int E_real, int align, int32_t* offsets,
+                           int32_t* src_rows, int32_t* pos, int32_t* tile_group, int tiles_cap, void* stream) {
   NVC_REQUIRE(ctx, ctx && topk_idx && offsets && src_rows && pos, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, E_real >= 0 && E_real <= E, NVC_EINVAL, "E_real must be in [0, E]");
   NVC_REQUIRE(ctx, N >= 0 && top > 0 && E > 0 && E <= 320 && align >= 1, NVC_EINVAL, "bad sizes");
   NVC_REQUIRE(ctx, !tile_group || (align > 1 && (int64_t)tiles_cap * align >= (int64_t)N * top + (int64_t)E * (align - 1)), NVC_EINVAL,
               "tile_group needs align > 1 and room for every group's padding");
   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_sort_kernel, dim3(1), dim3(1024), (size_t)(34 * E + 1) * sizeof(int32_t), nvc_stream(stream),
-                                 topk_idx, N * top, top, E, align, offsets, src_rows, pos, tile_group, tiles_cap));
+                                 topk_idx, N * top, top, E, E_real, align, offsets, src_rows, pos, tile_group, tiles_cap));
   ctx->launches++;
   return NVC_OK;
 }
@@ -330,6 +380,25 @@ int nvc_moe_combine(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int
   if (y_dtype == NVC_DT_F32 && shared_dtype == NVC_DT_F32) NVC_COMBINE(float, float);
   else if (y_dtype == NVC_DT_F32) NVC_COMBINE(float, __nv_bfloat16);
   else if (shared_dtype == NVC_DT_F32) NVC_COMBINE(__nv_bfloat16, float);
+  else NVC_COMBINE(__nv_bfloat16, __nv_bfloat16);
+#undef NVC_COMBINE
+  ctx->launches++;
+  return NVC_OK;
+}
+
+int nvc_moe_combine_identity(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, const int32_t* pos, const float* topk_w,
+                             const int32_t* topk_idx, int top, int E_real, const void* x, int x_dtype, int ldx, float* out, int ldo,
+                             int N, int H, void* stream) {
+  NVC_REQUIRE(ctx, ctx && y && pos && topk_w && topk_idx && x && out, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, N >= 0 && H > 0 && top > 0 && E_real >= 0 && ldy >= H && ldo >= H && ldx >= H, NVC_EINVAL, "bad sizes");
+  if (N == 0) return NVC_OK;
+  const dim3 grid(N), block(H >= 1024 ? 512 : 128);
+#define NVC_COMBINE(TY, TX)                                                                                                                  \
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_combine_identity_kernel<TY, TX>, grid, block, 0, nvc_stream(stream), reinterpret_cast<const TY*>(y), \
+                                 ldy, pos, topk_w, topk_idx, top, E_real, reinterpret_cast<const TX*>(x), ldx, out, ldo, H))
+  if (y_dtype == NVC_DT_F32 && x_dtype == NVC_DT_F32) NVC_COMBINE(float, float);
+  else if (y_dtype == NVC_DT_F32) NVC_COMBINE(float, __nv_bfloat16);
+  else if (x_dtype == NVC_DT_F32) NVC_COMBINE(__nv_bfloat16, float);
   else NVC_COMBINE(__nv_bfloat16, __nv_bfloat16);
 #undef NVC_COMBINE
   ctx->launches++;

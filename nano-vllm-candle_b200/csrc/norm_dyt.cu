@@ -46,7 +46,8 @@ template <typename T>
 __global__ void latent_norm_store_kernel(const float* __restrict__ in, int ldi, int n0, int off1, int n1,
                                          const float* __restrict__ w0, const float* __restrict__ w1, float eps,
                                          T* __restrict__ out0, int ld0, T* __restrict__ cache, int ldc,
-                                         const int32_t* __restrict__ slots, int N) {
+                                         const int32_t* __restrict__ slots, int rot_dim, int rot_dims, int rot_half,
+                                         const float* __restrict__ rot_table, const int32_t* __restrict__ positions, int N) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -65,11 +66,29 @@ __global__ void latent_norm_store_kernel(const float* __restrict__ in, int ldi, 
   ss = warp_sum(ss);
   r = 1.0f / sqrtf(ss / (float)n1 + eps);
   for (int j = lane; j < n1; j += 32) st_f(cache + (int64_t)slot * ldc + j, x[off1 + j] * r * __ldg(w1 + j));
+  // the key part that all heads share, behind the latent: turned by the token's position, not normed
+  const float* kr = x + off1 + n1;
+  const int half = rot_dims >> 1;
+  const float2* tab = reinterpret_cast<const float2*>(rot_table) + (int64_t)(rot_dims ? positions[row] : 0) * half;
+  for (int j = lane; j < rot_dim; j += 32) {
+    float y = kr[j];
+    if (j < rot_dims) {
+      int i, partner;
+      float sign;
+      if (rot_half) { i = j < half ? j : j - half; partner = j < half ? j + half : j - half; sign = j < half ? -1.f : 1.f; }
+      else { i = j >> 1; partner = j ^ 1; sign = (j & 1) ? 1.f : -1.f; }
+      const float2 cs = __ldg(tab + i);
+      y = y * cs.x + sign * kr[partner] * cs.y;
+    }
+    st_f(cache + (int64_t)slot * ldc + n1 + j, y);
+  }
 }
 
-// NVC_ACT_GELU_TANH_MUL: out[n, j] = gelu_tanh(in[n, j]) * in[n, Fp + j];  NVC_ACT_RELU2: out[n, j] = relu(in[n, j])^2
+// NVC_ACT_GELU_TANH_MUL: out[n, j] = gelu_tanh(in[n, j]) * in[n, Fp + j];  NVC_ACT_RELU2: out[n, j] = relu(in[n, j])^2;
+// NVC_ACT_GELU_TANH: gelu_tanh(in[n, j]);  NVC_ACT_GLU_CLAMP: g sigmoid(p1 g) (u + 1), g = min(in[n, j], p0), u = clamp(in[n, Fp + j], +-p0)
 template <typename T>
-__global__ void act_mul_kernel(const T* __restrict__ in, int ldi, T* __restrict__ out, int ldo, int N, int F, int Fp, int kind) {
+__global__ void act_mul_kernel(const T* __restrict__ in, int ldi, T* __restrict__ out, int ldo, int N, int F, int Fp, int kind, float p0,
+                               float p1) {
   pdl_trigger();
   pdl_wait();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -79,6 +98,12 @@ __global__ void act_mul_kernel(const T* __restrict__ in, int ldi, T* __restrict_
   float y;
   if (kind == NVC_ACT_GELU_TANH_MUL) {
     y = gelu_tanh_f32(g) * ld_f(in + (int64_t)n * ldi + Fp + j);
+  } else if (kind == NVC_ACT_GELU_TANH) {
+    y = gelu_tanh_f32(g);
+  } else if (kind == NVC_ACT_GLU_CLAMP) {
+    const float gc = fminf(g, p0);
+    const float u = fminf(fmaxf(ld_f(in + (int64_t)n * ldi + Fp + j), -p0), p0);
+    y = gc * sigmoid_f32(p1 * gc) * (u + 1.0f);
   } else {
     const float t = fmaxf(g, 0.f);
     y = t * t;
@@ -122,29 +147,48 @@ int nvc_dyt_norm(nvc_ctx* ctx, const float* res_in, const float* a0, const float
 int nvc_latent_norm_store(nvc_ctx* ctx, const float* in, int ldi, int n0, int off1, int n1, const float* w0, const float* w1,
                           float eps, void* out0, int ld0, void* cache, int ldc, const int32_t* slot_mapping, int dtype, int N,
                           void* stream) {
+  return nvc_latent_norm_store_rot(ctx, in, ldi, n0, off1, n1, w0, w1, eps, out0, ld0, cache, ldc, slot_mapping, 0, 0, 0, nullptr, nullptr,
+                                   dtype, N, stream);
+}
+
+int nvc_latent_norm_store_rot(nvc_ctx* ctx, const float* in, int ldi, int n0, int off1, int n1, const float* w0, const float* w1,
+                              float eps, void* out0, int ld0, void* cache, int ldc, const int32_t* slot_mapping, int rot_dim,
+                              int rot_dims, int rot_half, const float* rot_table, const int32_t* positions, int dtype, int N,
+                              void* stream) {
   NVC_REQUIRE(ctx, ctx && in && w0 && out0, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, rot_dim >= 0 && rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= rot_dim && (rot_dims == 0 || (rot_table && positions)),
+              NVC_EINVAL, "bad rotary arguments");
+  if (!cache) rot_dim = rot_dims = 0;
   NVC_REQUIRE(ctx, !cache || (w1 && slot_mapping), NVC_EINVAL, "a cache needs its norm weight and the slot mapping");
-  NVC_REQUIRE(ctx, N >= 0 && n0 > 0 && n1 >= 0 && off1 >= n0 && ldi >= off1 + n1 && ld0 >= n0 && (!cache || ldc >= n1), NVC_EINVAL,
-              "bad sizes");
+  NVC_REQUIRE(ctx, N >= 0 && n0 > 0 && n1 >= 0 && off1 >= n0 && ldi >= off1 + n1 + rot_dim && ld0 >= n0 && (!cache || ldc >= n1 + rot_dim),
+              NVC_EINVAL, "bad sizes");
   if (N == 0) return NVC_OK;
   NVC_DISPATCH_DT(dtype, T,
                   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, latent_norm_store_kernel<T>, dim3((N + 3) / 4), dim3(128), 0, nvc_stream(stream), in,
                                                  ldi, n0, off1, n1, w0, w1, eps, reinterpret_cast<T*>(out0), ld0,
-                                                 reinterpret_cast<T*>(cache), ldc, slot_mapping, N)));
+                                                 reinterpret_cast<T*>(cache), ldc, slot_mapping, rot_dim, rot_dims, rot_half, rot_table,
+                                                 positions, N)));
   ctx->launches++;
   return NVC_OK;
 }
 
 int nvc_act_mul(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int dtype, int N, int F, int Fp, int kind, void* stream) {
+  NVC_REQUIRE(ctx, kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_RELU2, NVC_EINVAL, "bad arguments");
+  return nvc_act_mul_p(ctx, in, ldi, out, ldo, dtype, N, F, Fp, kind, 0.f, 0.f, stream);
+}
+
+int nvc_act_mul_p(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int dtype, int N, int F, int Fp, int kind, float p0, float p1,
+                  void* stream) {
   NVC_REQUIRE(ctx, ctx && in && out, NVC_EINVAL, "null pointer");
-  NVC_REQUIRE(ctx, N >= 0 && F > 0 && (kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_RELU2), NVC_EINVAL, "bad arguments");
-  NVC_REQUIRE(ctx, ldo >= F && ldi >= (kind == NVC_ACT_GELU_TANH_MUL ? Fp + F : F), NVC_EINVAL, "bad strides");
+  const bool two = kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_GLU_CLAMP;
+  NVC_REQUIRE(ctx, N >= 0 && F > 0 && (two || kind == NVC_ACT_RELU2 || kind == NVC_ACT_GELU_TANH), NVC_EINVAL, "bad arguments");
+  NVC_REQUIRE(ctx, ldo >= F && ldi >= (two ? Fp + F : F), NVC_EINVAL, "bad strides");
   if (N == 0) return NVC_OK;
   const int64_t total = (int64_t)N * F;
   NVC_DISPATCH_DT(dtype, T,
                   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, act_mul_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
                                                  nvc_stream(stream), reinterpret_cast<const T*>(in), ldi, reinterpret_cast<T*>(out), ldo,
-                                                 N, F, Fp, kind)));
+                                                 N, F, Fp, kind, p0, p1)));
   ctx->launches++;
   return NVC_OK;
 }

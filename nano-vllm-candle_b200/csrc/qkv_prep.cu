@@ -85,6 +85,40 @@ __global__ void qkv_prep_kernel(const PrepArgs a) {
   }
 }
 
+
+// one warp per (token, head) of a query projection laid out [heads][dim | rot_dim]: the unrotated part goes to out_a, the rotated
+// part (turned by the token's position) to out_b
+template <typename T>
+__global__ void head_split_rot_kernel(const float* __restrict__ in, int ldi, int heads, int dim, int rot_dim, int rot_dims, int rot_half,
+                                      const float* __restrict__ rot_table, const int32_t* __restrict__ positions, T* __restrict__ out_a,
+                                      int ld_a, int hs_a, T* __restrict__ out_b, int ld_b, int hs_b, int off_b, int N) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (u >= (int64_t)N * heads) return;
+  const int n = (int)(u / heads), h = (int)(u % heads);
+  const float* x = in + (int64_t)n * ldi + (int64_t)h * (dim + rot_dim);
+  T* a = out_a + (int64_t)n * ld_a + (int64_t)h * hs_a;
+  for (int j = lane; j < dim; j += 32) st_f(a + j, x[j]);
+  const float* xr = x + dim;
+  T* b = out_b + (int64_t)n * ld_b + (int64_t)h * hs_b + off_b;
+  const int half = rot_dims >> 1;
+  const float2* tab = reinterpret_cast<const float2*>(rot_table) + (int64_t)(rot_dims ? positions[n] : 0) * half;
+  for (int j = lane; j < rot_dim; j += 32) {
+    float y = xr[j];
+    if (j < rot_dims) {
+      int i, partner;
+      float sign;
+      if (rot_half) { i = j < half ? j : j - half; partner = j < half ? j + half : j - half; sign = j < half ? -1.f : 1.f; }
+      else { i = j >> 1; partner = j ^ 1; sign = (j & 1) ? 1.f : -1.f; }
+      const float2 cs = __ldg(tab + i);
+      y = y * cs.x + sign * xr[partner] * cs.y;
+    }
+    st_f(b + j, y);
+  }
+}
+
 template <typename TQ, typename TKV>
 int launch_prep(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void* stream) {
   PrepArgs a{*p, N};
@@ -114,6 +148,25 @@ extern "C" int nvc_qkv_prep_run(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void
   if (p->q_dtype == NVC_DT_BF16 && p->kv_dtype == NVC_DT_BF16) return launch_prep<__nv_bfloat16, __nv_bfloat16>(ctx, p, N, stream);
   if (p->q_dtype == NVC_DT_BF16 && p->kv_dtype == NVC_DT_F32) return launch_prep<__nv_bfloat16, float>(ctx, p, N, stream);
   return launch_prep<float, __nv_bfloat16>(ctx, p, N, stream);
+}
+
+extern "C" int nvc_head_split_rot(nvc_ctx* ctx, const float* in, int ldi, int heads, int dim, int rot_dim, int rot_dims, int rot_half,
+                                  const float* rot_table, const int32_t* positions, void* out_a, int ld_a, int hs_a, void* out_b, int ld_b,
+                                  int hs_b, int off_b, int dtype, int N, void* stream) {
+  NVC_REQUIRE(ctx, ctx && in && out_a && out_b, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, N >= 0 && heads > 0 && dim > 0 && rot_dim >= 0 && ldi >= heads * (dim + rot_dim) && hs_a >= dim &&
+                       ld_a >= (heads - 1) * hs_a + dim && off_b >= 0 && hs_b >= off_b + rot_dim && ld_b >= (heads - 1) * hs_b + off_b + rot_dim,
+              NVC_EINVAL, "bad sizes");
+  NVC_REQUIRE(ctx, rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= rot_dim && (rot_dims == 0 || (rot_table && positions)), NVC_EINVAL,
+              "bad rotary arguments");
+  if (N == 0) return NVC_OK;
+  const int64_t units = (int64_t)N * heads;
+  NVC_DISPATCH_DT(dtype, T,
+                  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, head_split_rot_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, nvc_stream(stream),
+                                                 in, ldi, heads, dim, rot_dim, rot_dims, rot_half, rot_table, positions,
+                                                 reinterpret_cast<T*>(out_a), ld_a, hs_a, reinterpret_cast<T*>(out_b), ld_b, hs_b, off_b, N)));
+  ctx->launches++;
+  return NVC_OK;
 }
 
 // (cos, sin) of position * base^(-2 i / dims) for every position below max_pos and i < dims / 2, angles in double precision.
