@@ -115,6 +115,16 @@ def _declare(l: C.CDLL) -> None:
         "nvc_qkv_prep_run": [_vp, _vp, _i, _vp],
         "nvc_attn_paged_wide": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp],
         "nvc_retention_scan": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "nvc_rms_norm_sandwich": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _f, _vp, _i, _i, _vp],
+        "nvc_latent_norm_store_rot": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp],
+        "nvc_head_split_rot": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp],
+        "nvc_head_gate_w": [_vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
+        "nvc_act_mul_p": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp],
+        "nvc_moe_route_logits_ex": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+        "nvc_moe_sort_padded_ex": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp],
+        "nvc_moe_combine_identity": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _vp],
+        "nvc_delta_prep_run": [_vp, _vp, _i, _vp],
+        "nvc_delta_rule_scan": [_vp, _vp, _vp, _i, _vp, _i, _vp],
         "nvc_debug_set": [_i, _i],
     }
     for name, args in sigs.items():

@@ -1,4 +1,4 @@
-"""Karuzen or Ranilix beside the closest existing family (Qwen3, dense GQA) at equal layer sizes: prefill and decode throughput
+"""Karuzen, Ranilix or Fefozen beside the closest existing family (Qwen3, dense GQA) at equal layer sizes: prefill and decode throughput
 through LLMEngine, plus per-op times and roofline fractions.  Random weights, synthetic prompts.  Used by
 `bench.py --compare-families`; the default benchmark does not touch this module.
 
@@ -194,6 +194,141 @@ def ranilix_rooflines(cfg, prof: Dict[str, float], N: int, B: int, ctx_lens: Lis
     return out
 
 
+# ---- Fefozen at the same sizes: four layers - latent attention without sink (cache rows of 96 + 32 numbers: its long portions run
+# on the tcgen05 kernel), latent attention with a sink, a layer that reads the first layer's rows, a gated-delta-rule layer with
+# half as many key heads as heads - with a dense tanh-gelu feed-forward of 1.5 ff (two matrices: the gated one's parameter count)
+# or, in the mixture size, softmax-routed experts (two identity experts beside the real ones) behind the second and fourth mixer.
+F_KV_RANK, F_ROT, F_DIM = 96, 32, 96
+
+
+def fefozen_config(sz: dict) -> dict:
+    H, W = sz["heads"], sz["width"]
+
+    def latent(second, kv_from=None):
+        m = {"heads": H, "dim": F_DIM, "rot_dim": F_ROT, "vdim": 128, "kv_rank": F_KV_RANK, "q_rank": Q_RANK, "scale": (F_DIM + F_ROT) ** -0.5,
+             "rot": {"dims": F_ROT, "base": 10000.0}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention_2" if second else "latent_attention", "mixer": m}
+
+    delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": H // 2, "dim": 128, "vdim": 128, "conv": 4}}
+    dense = {"kind": "dense", "ff": sz["ff"] * 3 // 2}
+    if "moe" in sz:
+        m = sz["moe"]
+        moe = {"kind": "moe", "router": {"experts": m["experts"], "identity": 2, "top": m["top"]}, "expert": {"ff": m["expert_ff"], "limit": 7.0}}
+    else:
+        moe = dense
+    layers = [dict(latent(True), mlp=dict(dense)), dict(latent(False), mlp=dict(moe)), dict(latent(True, 0), mlp=dict(dense)), dict(delta, mlp=dict(moe))]
+    return {"architecture": "Fefozen", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "layers": [layers[i % 4] for i in range(sz["layers"])]}
+
+
+def fefozen_weights(cfg: dict, seed: int = 0):
+    """(name, bf16 CPU tensor) pairs, generated one at a time."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g) * i ** -0.5).bfloat16()
+
+    yield "embed", (torch.randn(cfg["vocab"], W, generator=g) * 0.05).bfloat16()
+    yield "final.norm", torch.zeros(W).bfloat16()
+    for i, ly in enumerate(cfg["layers"]):
+        m, p = ly["mixer"], f"l{i}."
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            yield p + n, torch.zeros(W).bfloat16()
+        if ly["type"] == "delta":
+            H, G, d, vd, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            for n, rows in (("q", G * d), ("k", G * d), ("v", H * vd)):
+                yield p + "mix." + n, mat(rows, W)
+                yield p + "mix." + n + ".conv", (torch.randn(rows, taps, generator=g) * 0.5).bfloat16()
+            yield p + "mix.b", mat(H, W)
+            yield p + "mix.a", mat(H, W)
+            yield p + "mix.A_log", torch.zeros(H).bfloat16()
+            yield p + "mix.dt_bias", torch.zeros(H).bfloat16()
+            yield p + "mix.norm", torch.ones(vd).bfloat16()
+            yield p + "mix.g", mat(H * vd, W)
+            yield p + "mix.o", mat(W, H * vd)
+        else:
+            H, d, rd, vd, kr, qr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            yield p + "mix.dq", mat(qr, W)
+            yield p + "mix.dq.norm", torch.ones(qr).bfloat16()
+            yield p + "mix.uq", mat(H * (d + rd), qr)
+            if m.get("kv_from") is None:
+                yield p + "mix.dkv", mat(kr + rd, W)
+                yield p + "mix.dkv.norm", torch.ones(kr).bfloat16()
+            yield p + "mix.uk", mat(H * d, kr)
+            yield p + "mix.uv", mat(H * vd, kr)
+            if ly["type"] == "latent_attention":
+                yield p + "mix.sink", torch.zeros(H).bfloat16()
+            yield p + "mix.g", mat(H * vd, W)
+            yield p + "mix.o", mat(W, H * vd)
+        f = ly["mlp"]
+        if f["kind"] == "dense":
+            yield p + "mlp.up", mat(f["ff"], W)
+            yield p + "mlp.down", mat(W, f["ff"])
+        else:
+            E, I, ef = f["router"]["experts"], f["router"]["identity"], f["expert"]["ff"]
+            yield p + "mlp.router", mat(E + I, W)
+            yield p + "mlp.correction", torch.zeros(E + I).bfloat16()
+            for e in range(E):
+                yield p + f"mlp.e{e}.gate", mat(ef, W)
+                yield p + f"mlp.e{e}.up", mat(ef, W)
+                yield p + f"mlp.e{e}.down", mat(W, ef)
+
+
+def fefozen_rooflines(cfg, prof: Dict[str, float], N: int, B: int, ctx_lens: List[int], q_lens: List[int], pk) -> dict:
+    """Per-op roofline of one profiled step: the times are sums over the layers, the work is summed the same way.  The delta-rule scan
+    runs on the fp32 FMA pipe (its state is fp32): its fraction is against that pipe's peak (pk["fp32"])."""
+    W = cfg["width"]
+    names = ("gemm_in", "gemm_uq", "absorb_uk", "attention", "absorb_uv", "gemm_o", "gemm_up", "gemm_down", "moe_gate_up", "moe_down", "delta_scan")
+    work = {k: [0.0, 0.0] for k in names}
+
+    def add(name, flops, nbytes):
+        work[name][0] += flops
+        work[name][1] += nbytes
+
+    pairs = sum(q * c - q * (q - 1) // 2 for q, c in zip(q_lens, ctx_lens))       # visible (query, key) pairs
+    for ly in cfg["layers"]:
+        m, f = ly["mixer"], ly["mlp"]
+        if ly["type"] == "delta":
+            H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            n_in, n_o = 2 * G * d + 2 * H * vd + 2 * H, H * vd
+            add("delta_scan", 6.0 * N * H * d * vd, 4.0 * (N * (2 * G * d + 2 * H * vd) + 2 * B * H * d * vd))
+        else:
+            H, d, rd, vd, kr, qr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            n_in, n_o = qr + (kr + rd if m.get("kv_from") is None else 0) + H * vd, H * vd
+            add("gemm_uq", 2.0 * N * H * (d + rd) * qr, 2.0 * (H * (d + rd) * qr + N * qr) + 4.0 * N * H * (d + rd))
+            add("absorb_uk", 2.0 * N * H * d * kr, 2.0 * (H * d * kr + N * H * (d + kr)))
+            add("absorb_uv", 2.0 * N * H * vd * kr, 2.0 * (H * vd * kr + N * H * kr) + 4.0 * N * H * vd)
+            add("attention", 2.0 * pairs * H * (2 * kr + rd), 2.0 * (sum(ctx_lens) * (kr + rd) + N * H * (2 * kr + rd)))
+        add("gemm_in", 2.0 * N * n_in * W, 2.0 * n_in * W + 2.0 * N * W + 4.0 * N * n_in)
+        add("gemm_o", 2.0 * N * n_o * W, 2.0 * n_o * W + 2.0 * N * n_o + 4.0 * N * W)
+        if f["kind"] == "dense":
+            add("gemm_up", 2.0 * N * f["ff"] * W, 2.0 * (f["ff"] * W + N * (f["ff"] + W)))
+            add("gemm_down", 2.0 * N * f["ff"] * W, 2.0 * (f["ff"] * W + N * f["ff"]) + 4.0 * N * W)
+        else:
+            E, I, top, ef = f["router"]["experts"], f["router"]["identity"], f["router"]["top"], f["expert"]["ff"]
+            real = N * top * E / (E + I)                                           # pairs that reach a real expert (uniform routing)
+            touched = min(E, N * top)
+            add("moe_gate_up", 4.0 * real * ef * W, 2.0 * (2 * touched * ef * W + real * (2 * ef + W)))
+            add("moe_down", 2.0 * real * ef * W, 2.0 * (touched * ef * W + real * ef) + 4.0 * real * W)
+    out = {}
+    for name, (fl, by) in work.items():
+        if name in prof and fl > 0:
+            if name == "delta_scan":
+                tmin = max(fl / (pk.get("fp32", 70.0) * 1e12), by / (pk["hbm"] * 1e9)) * 1e6
+                out[name] = {"us": round(prof[name], 2), "fp32_tflops": round(fl / prof[name] / 1e6, 2), "gbs": round(by / prof[name] / 1e3, 1),
+                             "roofline_frac": round(tmin / prof[name], 3)}
+            else:
+                out[name] = _roof(fl, by, prof[name], pk)
+    for name in ("norm", "latent_norm_store", "q_split_rot", "head_gate", "delta_prep", "moe_route", "moe_sort", "moe_gather", "moe_glu", "moe_combine",
+                 "embed", "final_norm", "lm_head"):
+        if name in prof:
+            out[name] = {"us": round(prof[name], 2)}
+    return out
+
+
 def _prompts(n, length, vocab, seed):
     rng = np.random.default_rng(seed)
     return [rng.integers(0, vocab, length).tolist() for _ in range(n)]
@@ -272,7 +407,8 @@ def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, p
     synth = importlib.import_module("nano-vllm-candle_b200.synth")
     pk = peaks or {"bf16": 1590.0, "hbm": 6650.0, "source": "fallback"}
     make_config, make_weights, rooflines = {"karuzen": (karuzen_config, karuzen_weights, karuzen_rooflines),
-                                            "ranilix": (ranilix_config, ranilix_weights, ranilix_rooflines)}[family]
+                                            "ranilix": (ranilix_config, ranilix_weights, ranilix_rooflines),
+                                            "fefozen": (fefozen_config, fefozen_weights, fefozen_rooflines)}[family]
     T = batch_p * plen
     nblocks = max(batch_p, batch_d) * (-(-(plen + W + K + 24) // BLOCK)) + 8
     results = []

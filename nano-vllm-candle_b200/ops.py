@@ -575,3 +575,114 @@ def retention_scan(ctx, q, k, v, state, state_slots, cu_seqlens, positions, deca
                                    _ptr(state_slots), _ptr(cu_seqlens), _ptr(positions), _ptr(decay), state_slots.numel(), max_qlen, heads, dim, vdim,
                                    _stream()), "nvc_retention_scan", ctx.h)
     return o
+
+
+# ---------------------------------------------------------------- sandwich norms, rotary latent rows, delta rule, softmax routing
+ACT_GELU_TANH, ACT_GLU_CLAMP = 3, 4
+ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
+
+
+class DeltaPrepC(C.Structure):
+    """nvc_delta_prep of include/nvc_b200.h."""
+    _fields_ = [("in_", C.c_void_p), ("ldi", C.c_int), ("q_off", C.c_int), ("k_off", C.c_int), ("v_off", C.c_int), ("b_off", C.c_int),
+                ("a_off", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("taps", C.c_int),
+                ("conv_w", C.c_void_p), ("conv_state", C.c_void_p), ("state_slots", C.c_void_p), ("cu_seqlens", C.c_void_p),
+                ("positions", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("unit_eps", C.c_float), ("q_scale", C.c_float),
+                ("q_out", C.c_void_p), ("k_out", C.c_void_p), ("v_out", C.c_void_p), ("ldq", C.c_int), ("ldk", C.c_int), ("ldv", C.c_int),
+                ("gb_out", C.c_void_p), ("B", C.c_int)]
+
+
+def rms_norm_sandwich(ctx, res, y, wy, w, eps: float = 1e-5, weight_offset: float = 1.0, out_dtype=torch.float32, rows=None,
+                      write_back: bool = True):
+    """(residual after the sum - a new tensor, or None when rows gather or write_back is False; the normed rows or None)."""
+    N = res.shape[0] if rows is None else rows.numel()
+    H = res.shape[1]
+    res_out = torch.empty_like(res) if (rows is None and write_back) else None
+    out = torch.empty(N, H, dtype=out_dtype, device=res.device) if w is not None else None
+    check(ctx.l.nvc_rms_norm_sandwich(ctx.h, _ptr(res), _ptr(y), _ptr(wy), _ptr(res_out), res.stride(0), _ptr(w), _ptr(out),
+                                      0 if out_dtype == torch.bfloat16 else 1, H, eps, weight_offset, _ptr(rows), N, H, _stream()),
+          "nvc_rms_norm_sandwich", ctx.h)
+    return res_out, out
+
+
+def latent_norm_store_rot(ctx, x, n0: int, off1: int, n1: int, w0, w1, eps: float, cache, slot_mapping, rot_dim: int, rot_dims: int,
+                          rot_half: bool, rot_table, positions, dtype):
+    """x: fp32 [N, ld]; returns the normed query latent [N, n0]; [normed latent | rotated part] goes to cache[slot]."""
+    N = x.shape[0]
+    out0 = torch.empty(N, n0, dtype=dtype, device=x.device)
+    check(ctx.l.nvc_latent_norm_store_rot(ctx.h, _ptr(x), x.stride(0), n0, off1, n1, _ptr(w0), _ptr(w1), eps, _ptr(out0), n0, _ptr(cache),
+                                          cache.stride(0) if cache is not None else 0, _ptr(slot_mapping), rot_dim, rot_dims,
+                                          1 if rot_half else 0, _ptr(rot_table), _ptr(positions), _dt(out0), N, _stream()),
+          "nvc_latent_norm_store_rot", ctx.h)
+    return out0
+
+
+def head_split_rot(ctx, x, heads: int, dim: int, rot_dim: int, rot_dims: int, rot_half: bool, rot_table, positions, out_a, hs_a: int, out_b,
+                   hs_b: int, off_b: int):
+    check(ctx.l.nvc_head_split_rot(ctx.h, _ptr(x), x.stride(0), heads, dim, rot_dim, rot_dims, 1 if rot_half else 0, _ptr(rot_table),
+                                   _ptr(positions), _ptr(out_a), out_a.stride(0), hs_a, _ptr(out_b), out_b.stride(0), hs_b, off_b, _dt(out_a),
+                                   x.shape[0], _stream()), "nvc_head_split_rot", ctx.h)
+
+
+def head_gate_w(ctx, o, gate, weight, heads: int, vdim: int, norm: bool, eps: float, act: str, out_scale: float, out_dtype=torch.float32):
+    out = torch.empty(o.shape[0], heads * vdim, dtype=out_dtype, device=o.device)
+    check(ctx.l.nvc_head_gate_w(ctx.h, _ptr(o), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight), _ptr(out),
+                                out.stride(0), 0 if out_dtype == torch.bfloat16 else 1, heads, vdim, 1 if norm else 0, eps,
+                                {"sigmoid": 0, "silu": 1}[act], out_scale, o.shape[0], _stream()), "nvc_head_gate_w", ctx.h)
+    return out
+
+
+def act_mul_p(ctx, x, F: int, Fp: int, kind: int, p0: float = 0.0, p1: float = 0.0):
+    N = x.shape[0]
+    out = torch.empty(N, F, dtype=x.dtype, device=x.device)
+    check(ctx.l.nvc_act_mul_p(ctx.h, _ptr(x), x.stride(0), _ptr(out), F, _dt(x), N, F, Fp, kind, p0, p1, _stream()), "nvc_act_mul_p", ctx.h)
+    return out
+
+
+def moe_route_logits_ex(ctx, z, correction, E: int, top: int, scale: float, score: int, normalize: bool):
+    N = z.shape[0]
+    idx = torch.empty(N, top, dtype=torch.int32, device=z.device)
+    w = torch.empty(N, top, dtype=torch.float32, device=z.device)
+    check(ctx.l.nvc_moe_route_logits_ex(ctx.h, _ptr(z), z.stride(0), _ptr(correction), E, top, scale, -1, score, 1 if normalize else 0, _ptr(idx),
+                                        _ptr(w), None, N, _stream()), "nvc_moe_route_logits_ex", ctx.h)
+    return idx, w
+
+
+def moe_sort_padded_ex(ctx, idx, E: int, E_real: int, align: int = 128):
+    N, top = idx.shape
+    tiles = (N * top + E * (align - 1) + align - 1) // align
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=idx.device)
+    src = torch.full((tiles * align,), -7, dtype=torch.int32, device=idx.device)
+    pos = torch.empty(N * top, dtype=torch.int32, device=idx.device)
+    tile_group = torch.full((tiles,), -7, dtype=torch.int32, device=idx.device)
+    check(ctx.l.nvc_moe_sort_padded_ex(ctx.h, _ptr(idx), N, top, E, E_real, align, _ptr(offsets), _ptr(src), _ptr(pos), _ptr(tile_group), tiles,
+                                       _stream()), "nvc_moe_sort_padded_ex", ctx.h)
+    return offsets, src, pos, tile_group
+
+
+def moe_combine_identity(ctx, y, pos, w, idx, E_real: int, x):
+    N, top = w.shape
+    H = x.shape[1]
+    out = torch.empty(N, H, dtype=torch.float32, device=y.device)
+    check(ctx.l.nvc_moe_combine_identity(ctx.h, _ptr(y), _dt(y), y.stride(0), _ptr(pos), _ptr(w), _ptr(idx), top, E_real, _ptr(x), _dt(x),
+                                         x.stride(0), _ptr(out), H, N, H, _stream()), "nvc_moe_combine_identity", ctx.h)
+    return out
+
+
+def delta_rule(ctx, x, offs, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, conv_w, conv_state, state, state_slots, cu_seqlens,
+               positions, A_log, dt_bias, unit_eps: float = 1e-6, q_scale: Optional[float] = None, max_qlen: int = 1 << 20):
+    """x: fp32 [N, ld] rows of the fused projection, offs = (q, k, v, beta, a) columns.  Runs the preparation and the recurrence;
+    conv_state [slots, taps - 1, C] and state [slots, heads, dim, vdim] are updated in place.  Returns (o [N, heads * vdim], q, k, v, gb)."""
+    N = x.shape[0]
+    dev = x.device
+    q = torch.empty(N, kv_heads * dim, dtype=torch.float32, device=dev)
+    k = torch.empty_like(q)
+    v = torch.empty(N, heads * vdim, dtype=torch.float32, device=dev)
+    gb = torch.empty(N, 2 * heads, dtype=torch.float32, device=dev)
+    o = torch.empty(N, heads * vdim, dtype=torch.float32, device=dev)
+    p = DeltaPrepC(_a(x), x.stride(0), offs[0], offs[1], offs[2], offs[3], offs[4], heads, kv_heads, dim, vdim, taps, _a(conv_w), _a(conv_state),
+                   _a(state_slots), _a(cu_seqlens), _a(positions), _a(A_log), _a(dt_bias), unit_eps, dim ** -0.5 if q_scale is None else q_scale,
+                   _a(q), _a(k), _a(v), q.stride(0), k.stride(0), v.stride(0), _a(gb), state_slots.numel())
+    check(ctx.l.nvc_delta_prep_run(ctx.h, C.byref(p), N, _stream()), "nvc_delta_prep_run", ctx.h)
+    check(ctx.l.nvc_delta_rule_scan(ctx.h, C.byref(p), _ptr(o), o.stride(0), _ptr(state), max_qlen, _stream()), "nvc_delta_rule_scan", ctx.h)
+    return o, q, k, v, gb

@@ -214,9 +214,11 @@ class Fefozen:
     def new_cache(self) -> dict:
         return {"len": 0, "rows": {}, "state": {}}
 
-    def forward(self, tokens: List[int], cache: dict, taps: Optional[list] = None) -> torch.Tensor:
-        """Runs T new tokens of one request on top of `cache`; returns logits [T, V]."""
+    def forward(self, tokens: List[int], cache: Optional[dict] = None, taps: Optional[list] = None) -> torch.Tensor:
+        """Runs T new tokens of one request on top of `cache` (None: a whole prompt from an empty cache); returns logits [T, V]."""
         cfg, eps = self.cfg, self.eps
+        if cache is None:
+            cache = self.new_cache()
         pos0 = cache["len"]
         x = self.p["embed"][torch.tensor(tokens)]
         for i, ly in enumerate(cfg["layers"]):
@@ -246,3 +248,93 @@ class Fefozen:
                 taps.append(x.clone())
         cache["len"] = pos0 + len(tokens)
         return zero_centred_norm(x, self.p["final.norm"], eps) @ self.p["embed"].T
+
+
+# ------------------------------------------------------------------------------------------ small configurations
+
+def latent_cfg(heads=4, dim=16, rot_dim=8, vdim=24, kv_rank=40, q_rank=48, scale=0.2, rot_dims=None, rot_base=10000.0, second=False,
+               kv_from=None) -> dict:
+    """second: the kind with rotate-half pairs and a plain softmax (it may read another layer's rows); else interleaved pairs and a sink."""
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale,
+         "rot": {"dims": rot_dim if rot_dims is None else rot_dims, "base": rot_base}}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "latent_attention_2" if second else "latent_attention", "mixer": m}
+
+
+def delta_cfg(heads=4, kv_heads=2, dim=16, vdim=24, conv=4) -> dict:
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}}
+
+
+def with_dense(layer: dict, ff: Optional[int] = 96) -> dict:
+    layer = dict(layer)
+    layer["mlp"] = {"kind": "dense", "ff": ff} if ff else None
+    return layer
+
+
+def with_moe(layer: dict, experts=5, identity=2, top=2, ff=40, limit=1.0) -> dict:
+    layer = dict(layer)
+    layer["mlp"] = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top}, "expert": {"ff": ff, "limit": limit}}
+    return layer
+
+
+def make_config(vocab=200, width=96, layers=None, eps=1e-5) -> dict:
+    return {"architecture": "Fefozen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+
+
+def make_weights(cfg: dict, seed: int = 0, bf16_values: bool = True) -> Dict[str, torch.Tensor]:
+    """Random weights under the checkpoint's names; values bf16-representable by default so that the bf16 and fp32 paths load
+    identical numbers.  Corrections move some of the routers' choices."""
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+
+    def fix(t):
+        return t.bfloat16().float() if bf16_values else t
+
+    def rnd(*shape, s=1.0):
+        return fix(torch.randn(*shape, generator=g) * s)
+
+    w = {"embed": rnd(cfg["vocab"], W, s=1.0), "final.norm": rnd(W, s=0.2)}
+    for i, ly in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", ly["mixer"]
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if ly.get("mlp") else ()):
+            w[p + n] = rnd(W, s=0.2)
+        if ly["type"].startswith("latent_attention"):
+            H, d, rd, vd, R, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            w[p + "mix.dq"] = rnd(Q, W, s=W ** -0.5)
+            w[p + "mix.dq.norm"] = fix(1.0 + rnd(Q, s=0.2))
+            w[p + "mix.uq"] = rnd(H * (d + rd), Q, s=Q ** -0.5)
+            if m.get("kv_from") is None:
+                w[p + "mix.dkv"] = rnd(R + rd, W, s=W ** -0.5)
+                w[p + "mix.dkv.norm"] = fix(1.0 + rnd(R, s=0.2))
+            w[p + "mix.uk"] = rnd(H * d, R, s=R ** -0.5)
+            w[p + "mix.uv"] = rnd(H * vd, R, s=R ** -0.5)
+            if ly["type"] == "latent_attention":
+                w[p + "mix.sink"] = rnd(H, s=1.0)
+            w[p + "mix.g"] = rnd(H * vd, W, s=W ** -0.5)
+            w[p + "mix.o"] = rnd(W, H * vd, s=(H * vd) ** -0.5)
+        else:
+            H, G, d, vd, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            for n, rows in (("q", G * d), ("k", G * d), ("v", H * vd)):
+                w[p + "mix." + n] = rnd(rows, W, s=W ** -0.5)
+                w[p + "mix." + n + ".conv"] = rnd(rows, taps, s=taps ** -0.5)
+            w[p + "mix.b"] = rnd(H, W, s=W ** -0.5)
+            w[p + "mix.a"] = rnd(H, W, s=W ** -0.5)
+            w[p + "mix.A_log"] = fix(torch.log(0.5 + 2.0 * torch.rand(H, generator=g)))
+            w[p + "mix.dt_bias"] = rnd(H, s=0.5)
+            w[p + "mix.norm"] = fix(1.0 + rnd(vd, s=0.2))
+            w[p + "mix.g"] = rnd(H * vd, W, s=W ** -0.5)
+            w[p + "mix.o"] = rnd(W, H * vd, s=(H * vd) ** -0.5)
+        f = ly.get("mlp")
+        if f and f["kind"] == "dense":
+            w[p + "mlp.up"] = rnd(f["ff"], W, s=W ** -0.5)
+            w[p + "mlp.down"] = rnd(W, f["ff"], s=f["ff"] ** -0.5)
+        elif f:
+            E, I, ff = f["router"]["experts"], f["router"].get("identity", 0), f["expert"]["ff"]
+            w[p + "mlp.router"] = rnd(E + I, W, s=W ** -0.5)
+            w[p + "mlp.correction"] = rnd(E + I, s=0.1)
+            for e in range(E):
+                w[p + f"mlp.e{e}.gate"] = rnd(ff, W, s=2.0 * W ** -0.5)
+                w[p + f"mlp.e{e}.up"] = rnd(ff, W, s=2.0 * W ** -0.5)
+                w[p + f"mlp.e{e}.down"] = rnd(W, ff, s=ff ** -0.5)
+    return w
