@@ -502,7 +502,7 @@ int nvc_moe_combine_identity(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, 
  *   q and k heads: x / sqrt(sum(x^2) + unit_eps), q times q_scale;   beta = sigmoid(in[b_off + h]);
  *   decay = exp(-exp(A_log[h]) * softplus(in[a_off + h] + dt_bias[h])).
  * Channel order of conv_w and conv_state: q (kv_heads * dim), k (kv_heads * dim), v (heads * vdim).  Outputs are fp32 rows;
- * gb_out [N, 2 * heads] = (decay, beta) per head.  The conv state is NOT advanced here (nvc_delta_rule_scan does it). */
+ * gb_out [N, 2 * heads] = (log decay, beta) per head.  The conv state is NOT advanced here (nvc_delta_rule_scan does it). */
 typedef struct nvc_delta_prep {
   const float* in; int ldi;
   int q_off, k_off, v_off, b_off, a_off;
@@ -520,7 +520,8 @@ int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, void* strea
 /* The recurrence, per (sequence, head) with state S [dim, vdim] fp32 in state [slots, heads, dim, vdim]:
  *   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q        (head h reads q / k head h / (heads / kv_heads))
  * token by token over rows cu_seqlens[b] .. cu_seqlens[b + 1] (row b when cu_seqlens == NULL); a sequence starts from zeros when
- * positions[first row] == 0.  Also advances the convolution state of nvc_delta_prep_run (p->in still holds the step's rows). */
+ * positions[first row] == 0; portions of 8 tokens and more (max_qlen) run 32 tokens at a time (the same sums regrouped, fp32 FMA).
+ * Also advances the convolution state of nvc_delta_prep_run (p->in still holds the step's rows). */
 int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float* o, int ldo, float* state, int max_qlen, void* stream);
 
 /* K8. Replaces Qwen3ModelRunner::argmax (src/engine/llm_engine.rs:135-142) on device:

@@ -1,7 +1,7 @@
 // The gated delta rule: a linear-attention mixer whose per-head state S [dim, vdim] is decayed, corrected towards the new value
 // and read in every token,
 //   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q,
-// with q, k, v taken through a short causal convolution over time per channel.  Two kernels:
+// with q, k, v taken through a short causal convolution over time per channel.  Three kernels:
 //   delta_prep_kernel   one warp per (token, unit): convolution + silu of a q / k / v head (the taps - 1 inputs in front of a
 //                       portion come from the sequence's convolution state), unit length for q and k, q scale; one more unit per token
 //                       for the per-head decay g = exp(-exp(A_log) softplus(a + dt_bias)) and beta = sigmoid(b)
@@ -10,7 +10,8 @@
 //                       the state per token: with a = S^T k, c = S^T q of the state BEFORE the token and kq = k . q,
 //                           u = beta (v - g a),   o = g c + kq u,   S <- g S + k u^T
 //                       (the same sums as the four steps above, regrouped so that a token needs one reduction over row groups).
-//                       The CTAs of head 0, slice 0 also advance the convolution state of their sequence.
+//                       The CTAs of a sequence also advance its convolution state, a share of the channels each.
+//   delta_chunk_kernel  the same recurrence 32 tokens at a time for prompt portions (see there).
 // Both states live in fp32 in pools of state slots; a sequence whose first new token sits at position 0 starts from zeros.
 // Everything here is plain fp32 FMA code.
 #include "typed.cuh"
@@ -50,7 +51,7 @@ __global__ void delta_prep_kernel(const DeltaArgs a) {
     // ---- decay and beta of every head
     for (int h = lane; h < p.heads; h += 32) {
       const float dt = softplus_f32(in[p.a_off + h] + __ldg(p.dt_bias + h));
-      p.gb_out[(int64_t)n * 2 * p.heads + 2 * h] = expf(-expf(__ldg(p.A_log + h)) * dt);
+      p.gb_out[(int64_t)n * 2 * p.heads + 2 * h] = -expf(__ldg(p.A_log + h)) * dt;       // log of the decay
       p.gb_out[(int64_t)n * 2 * p.heads + 2 * h + 1] = sigmoid_f32(in[p.b_off + h]);
     }
     return;
@@ -96,6 +97,28 @@ __global__ void delta_prep_kernel(const DeltaArgs a) {
   for (int j = lane; j < width; j += 32) out[j] *= r;
 }
 
+
+// The convolution state of a sequence after a portion: the last taps - 1 inputs of (what it held, this portion).  Slot i reads slot
+// i + len or the portion, never a slot below itself, so one thread per channel shifts in place.  The channels are spread over the
+// CTAs (head, value slice) of the sequence; nothing else in a scan kernel reads this state.
+__device__ __forceinline__ void advance_conv_state(const nvc_delta_prep& p, int r0, int r1, bool fresh, int slot) {
+  const int C = 2 * p.kv_heads * p.dim + p.heads * p.vdim, len = r1 - r0, keep = p.taps - 1;
+  if (keep == 0) return;
+  float* cs = p.conv_state + (int64_t)slot * keep * C;
+  const int part = blockIdx.y * gridDim.z + blockIdx.z, parts = gridDim.y * gridDim.z;
+  const int qk = p.kv_heads * p.dim;
+  for (int c = part * blockDim.x + threadIdx.x; c < C; c += parts * blockDim.x) {
+    const int col = c < qk ? p.q_off + c : (c < 2 * qk ? p.k_off + c - qk : p.v_off + c - 2 * qk);
+    for (int i = 0; i < keep; ++i) {
+      const int src = len - keep + i;                 // portion index
+      float x;
+      if (src >= 0) x = p.in[(int64_t)(r0 + src) * p.ldi + col];
+      else x = fresh ? 0.f : cs[(int64_t)(keep + src) * C + c];
+      cs[(int64_t)i * C + c] = x;
+    }
+  }
+}
+
 template <int DPT>
 __global__ void delta_scan_kernel(const DeltaArgs a) {
   extern __shared__ float sm[];
@@ -114,23 +137,7 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
   const int r1 = p.cu_seqlens ? p.cu_seqlens[b + 1] : b + 1;
   const bool fresh = p.positions[r0] == 0;
   const int slot = p.state_slots[b];
-  if (h == 0 && blockIdx.z == 0) {
-    // ---- the convolution state of this sequence: the last taps - 1 inputs of (what it held, this portion); slot i reads slot
-    // i + len or the portion, never a slot below itself, so one thread per channel can shift in place
-    const int C = 2 * p.kv_heads * p.dim + p.heads * p.vdim, len = r1 - r0, keep = p.taps - 1;
-    float* cs = p.conv_state + (int64_t)slot * keep * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      const int qk = p.kv_heads * p.dim;
-      const int col = c < qk ? p.q_off + c : (c < 2 * qk ? p.k_off + c - qk : p.v_off + c - 2 * qk);
-      for (int i = 0; i < keep; ++i) {
-        const int src = len - keep + i;                 // portion index
-        float x;
-        if (src >= 0) x = p.in[(int64_t)(r0 + src) * p.ldi + col];
-        else x = fresh ? 0.f : cs[(int64_t)(keep + src) * C + c];
-        cs[(int64_t)i * C + c] = x;
-      }
-    }
-  }
+  advance_conv_state(p, r0, r1, fresh, slot);
   const int d0 = rg * DPT;
   float S[DPT];
   float* sp = a.state + (((int64_t)slot * p.heads + h) * p.dim) * p.vdim;
@@ -141,7 +148,7 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
     k_s[d] = p.k_out[(int64_t)r0 * p.ldk + hk * p.dim + d];
   }
   float vt = vok ? p.v_out[(int64_t)r0 * p.ldv + h * p.vdim + v] : 0.f;
-  float gt = p.gb_out[(int64_t)r0 * 2 * p.heads + 2 * h], bt = p.gb_out[(int64_t)r0 * 2 * p.heads + 2 * h + 1];
+  float gt = expf(p.gb_out[(int64_t)r0 * 2 * p.heads + 2 * h]), bt = p.gb_out[(int64_t)r0 * 2 * p.heads + 2 * h + 1];
   __syncthreads();
   for (int t = r0; t < r1; ++t) {
     const int cur = (t - r0) & 1;
@@ -154,7 +161,7 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
         k_s[(cur ^ 1) * p.dim + d] = p.k_out[(int64_t)(t + 1) * p.ldk + hk * p.dim + d];
       }
       vn = vok ? p.v_out[(int64_t)(t + 1) * p.ldv + h * p.vdim + v] : 0.f;
-      gn = p.gb_out[(int64_t)(t + 1) * 2 * p.heads + 2 * h];
+      gn = expf(p.gb_out[(int64_t)(t + 1) * 2 * p.heads + 2 * h]);
       bn = p.gb_out[(int64_t)(t + 1) * 2 * p.heads + 2 * h + 1];
     }
     float sk = 0.f, sq = 0.f, kq = 0.f;
@@ -193,6 +200,180 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
       if (d0 + i < p.dim) sp[(int64_t)(d0 + i) * p.vdim + v] = S[i];
 }
 
+
+// ---- prompt portions: 32 tokens at a time.  Within a chunk that starts from the state S0, with L_t the running sum of log g up to
+// token t (so exp(L_t - L_j) is the decay between tokens j and t),
+//   u_t = beta_t (v_t - exp(L_t) S0^T k_t - sum_{j<t} exp(L_t - L_j) (k_j . k_t) u_j)        a triangular system, solved forwards
+//   o_t = exp(L_t) S0^T q_t + sum_{j<=t} exp(L_t - L_j) (k_j . q_t) u_j
+//   S   = exp(L_n) S0 + sum_j exp(L_n - L_j) k_j u_j^T
+// which are the four steps of the recurrence written out over the chunk; only differences L_t - L_j <= 0 are exponentiated, so a
+// decay that underflows over a chunk stays a plain zero.  One CTA of four warps per (sequence, head, 32 value columns); thread
+// (column v, warp w) keeps rows [w DPT, (w + 1) DPT) of column v of the state in registers.  Tokens behind a portion's end are
+// padded with g = 1, beta = 0, k = q = v = 0, which leaves state and outputs alone.
+constexpr int kDC = 32;
+constexpr int kDW = 4;
+
+__host__ __device__ inline size_t delta_chunk_smem_floats(int dim) {
+  return (size_t)2 * kDC * (dim + 1) + 2 * kDC * (kDC + 1) + 3 * kDC * 32 + (size_t)kDW * kDC * 32 + 2 * kDC + 8;
+}
+
+template <int DPT>
+__global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  const nvc_delta_prep& p = a.p;
+  const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int v = v0 + lane;
+  const bool vok = v < p.vdim;
+  const int hk = h / (p.heads / p.kv_heads);
+  const int dim = p.dim, ds = dim + 1, as = kDC + 1;
+  float* Ks = sm;                          // [kDC][ds]
+  float* Qs = Ks + kDC * ds;               // [kDC][ds]
+  float* Am = Qs + kDC * ds;               // [kDC][as]  beta_t exp(L_t - L_j) (k_t . k_j), j < t
+  float* Pm = Am + kDC * as;               // [kDC][as]  exp(L_t - L_j) (q_t . k_j), j <= t
+  float* Us = Pm + kDC * as;               // [kDC][32]  v_t, then u_t
+  float* W1 = Us + kDC * 32;               // [kDC][32]  S0^T k_t
+  float* W2 = W1 + kDC * 32;               // [kDC][32]  S0^T q_t
+  float* Wp = W2 + kDC * 32;               // [kDW][kDC][32] partial sums of the row groups
+  float* Ls = Wp + kDW * kDC * 32;         // [kDC]
+  float* Bs = Ls + kDC;                    // [kDC]
+  pdl_wait();
+  const int r0 = p.cu_seqlens ? p.cu_seqlens[b] : b;
+  const int r1 = p.cu_seqlens ? p.cu_seqlens[b + 1] : b + 1;
+  const bool fresh = p.positions[r0] == 0;
+  const int slot = p.state_slots[b];
+  advance_conv_state(p, r0, r1, fresh, slot);
+  const int d0 = w * DPT;
+  float S[DPT];
+  float* sp = a.state + (((int64_t)slot * p.heads + h) * dim) * p.vdim;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) S[i] = (!fresh && vok && d0 + i < dim) ? sp[(int64_t)(d0 + i) * p.vdim + v] : 0.f;
+  for (int c0 = r0; c0 < r1; c0 += kDC) {
+    const int n = min(kDC, r1 - c0);
+    // ---- stage the chunk
+    for (int idx = threadIdx.x; idx < kDC * dim; idx += kDW * 32) {
+      const int t = idx / dim, c = idx - t * dim;
+      Ks[t * ds + c] = t < n ? p.k_out[(int64_t)(c0 + t) * p.ldk + hk * dim + c] : 0.f;
+      Qs[t * ds + c] = t < n ? p.q_out[(int64_t)(c0 + t) * p.ldq + hk * dim + c] : 0.f;
+    }
+    for (int t = w; t < kDC; t += kDW) Us[t * 32 + lane] = (t < n && vok) ? p.v_out[(int64_t)(c0 + t) * p.ldv + h * p.vdim + v] : 0.f;
+    if (w == 0) {
+      float lg = lane < n ? p.gb_out[(int64_t)(c0 + lane) * 2 * p.heads + 2 * h] : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, lg, o);
+        if (lane >= o) lg += up;
+      }
+      Ls[lane] = lg;
+      Bs[lane] = lane < n ? p.gb_out[(int64_t)(c0 + lane) * 2 * p.heads + 2 * h + 1] : 0.f;
+    }
+    __syncthreads();
+    // ---- products between the chunk's tokens (row t per warp, column j per lane)
+    for (int t = w; t < kDC; t += kDW) {
+      float kk = 0.f, qk = 0.f;
+      if (lane <= t) {
+        const float* kt = Ks + t * ds;
+        const float* qt = Qs + t * ds;
+        const float* kj = Ks + lane * ds;
+#pragma unroll 4
+        for (int c = 0; c < dim; ++c) {
+          const float x = kj[c];
+          kk = fmaf(kt[c], x, kk);
+          qk = fmaf(qt[c], x, qk);
+        }
+        const float e = expf(Ls[t] - Ls[lane]);
+        kk *= e * Bs[t];
+        qk *= e;
+      }
+      Am[t * as + lane] = lane < t ? kk : 0.f;
+      Pm[t * as + lane] = lane <= t ? qk : 0.f;
+    }
+    // ---- what the state before the chunk says to every key and query: partial sums over this warp's rows, then over the warps
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+      const float* X = pass == 0 ? Ks : Qs;
+      float* Wd = pass == 0 ? W1 : W2;
+#pragma unroll 1
+      for (int t0 = 0; t0 < kDC; t0 += 8) {
+        float acc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+          if (d0 + i < dim) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[u] = fmaf(S[i], X[(t0 + u) * ds + d0 + i], acc[u]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) Wp[(w * kDC + t0 + u) * 32 + lane] = acc[u];
+      }
+      __syncthreads();
+      for (int t = w; t < kDC; t += kDW) {
+        float s = 0.f;
+#pragma unroll
+        for (int g = 0; g < kDW; ++g) s += Wp[(g * kDC + t) * 32 + lane];
+        Wd[t * 32 + lane] = s;
+      }
+      __syncthreads();
+    }
+    // ---- the triangular system, one value column per lane of warp 0
+    if (w == 0) {
+      float u[kDC];
+#pragma unroll
+      for (int t = 0; t < kDC; ++t) {
+        float x = Bs[t] * (Us[t * 32 + lane] - expf(Ls[t]) * W1[t * 32 + lane]);
+#pragma unroll
+        for (int j = 0; j < t; ++j) x = fmaf(-Am[t * as + j], u[j], x);
+        u[t] = x;
+      }
+#pragma unroll
+      for (int t = 0; t < kDC; ++t) Us[t * 32 + lane] = u[t];
+    }
+    __syncthreads();
+    // ---- outputs
+    for (int t = w; t < n; t += kDW) {
+      float o = expf(Ls[t]) * W2[t * 32 + lane];
+      for (int j = 0; j <= t; ++j) o = fmaf(Pm[t * as + j], Us[j * 32 + lane], o);
+      if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * p.vdim + v] = o;
+    }
+    // ---- the state behind the chunk
+    {
+      const float Ln = Ls[kDC - 1];
+      const float gn = expf(Ln);
+      float uu[kDC];
+#pragma unroll
+      for (int j = 0; j < kDC; ++j) uu[j] = expf(Ln - Ls[j]) * Us[j * 32 + lane];
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        if (d0 + i < dim) {
+          float s = gn * S[i];
+#pragma unroll
+          for (int j = 0; j < kDC; ++j) s = fmaf(Ks[j * ds + d0 + i], uu[j], s);
+          S[i] = s;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (vok)
+#pragma unroll
+    for (int i = 0; i < DPT; ++i)
+      if (d0 + i < dim) sp[(int64_t)(d0 + i) * p.vdim + v] = S[i];
+}
+
+template <int DPT>
+cudaError_t launch_delta_chunk(nvc_ctx* ctx, const DeltaArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_chunk_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  return nvc_launch(ctx, delta_chunk_kernel<DPT>, grid, dim3(kDW * 32), smem, st, a);
+}
+
 int check_prep(nvc_ctx* ctx, const nvc_delta_prep* p) {
   NVC_REQUIRE(ctx, ctx && p && p->in && p->conv_w && p->conv_state && p->state_slots && p->positions && p->A_log && p->dt_bias && p->q_out &&
                        p->k_out && p->v_out && p->gb_out, NVC_EINVAL, "null pointer");
@@ -222,6 +403,21 @@ extern "C" int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float*
   NVC_REQUIRE(ctx, o && state && ldo >= p->heads * p->vdim && max_qlen >= 1, NVC_EINVAL, "bad output / state");
   DeltaArgs a{*p, 0, o, ldo, state};
   const int dim = p->dim;
+  if (p->cu_seqlens && max_qlen >= 8 && dim <= 512 && delta_chunk_smem_floats(dim) * sizeof(float) <= 200 * 1024) {
+    // prompt portions: 32 tokens at a time
+    const int per = (dim + kDW - 1) / kDW;     // rows of the state per warp
+    const dim3 grid(p->B, p->heads, (p->vdim + 31) / 32);
+    const size_t smem = delta_chunk_smem_floats(dim) * sizeof(float);
+    cudaError_t ce;
+    if (per <= 8) ce = launch_delta_chunk<8>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 16) ce = launch_delta_chunk<16>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 32) ce = launch_delta_chunk<32>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 64) ce = launch_delta_chunk<64>(ctx, a, grid, smem, nvc_stream(stream));
+    else ce = launch_delta_chunk<128>(ctx, a, grid, smem, nvc_stream(stream));
+    NVC_CUDA_CHECK(ctx, ce);
+    ctx->launches++;
+    return NVC_OK;
+  }
   const int dpt = dim <= 16 ? 16 : (dim <= 32 ? 32 : (dim <= 64 ? 64 : 128));
   const int groups = (dim + dpt - 1) / dpt;
   const dim3 grid(p->B, p->heads, (p->vdim + 31) / 32), block(32 * groups);

@@ -255,8 +255,10 @@ def plain_delta(x, offs, H, G, d, vd, conv_w, A_log, dt_bias, state):
     return o.reshape(T, H * vd), (S, torch.cat(keep, -1))
 
 
+@pytest.mark.parametrize("form", ["token by token", "chunks"])
 @pytest.mark.parametrize("H,G,d,vd,taps", [(4, 2, 16, 24, 4), (3, 3, 10, 36, 2), (2, 1, 64, 64, 3), (2, 2, 200, 8, 1), (1, 1, 128, 40, 5)])
-def test_delta_rule_carries_both_states_between_portions_and_slots(ctx, ops, H, G, d, vd, taps):
+def test_delta_rule_carries_both_states_between_portions_and_slots(ctx, ops, H, G, d, vd, taps, form):
+    max_qlen = 1 if form == "token by token" else 64
     g = torch.Generator().manual_seed(14)
     slots, qk = 4, G * d
     C = 2 * qk + H * vd
@@ -285,7 +287,7 @@ def test_delta_rule_carries_both_states_between_portions_and_slots(ctx, ops, H, 
             pos += list(range(lo, lo + c))
             cu.append(cu[-1] + c)
         o = ops.delta_rule(ctx, torch.cat(xs).to(DEV), offs, state_slots=i32([slot_of[n] for n, _ in step]), cu_seqlens=i32(cu), positions=i32(pos),
-                           **kw)[0].cpu()
+                           max_qlen=max_qlen, **kw)[0].cpu()
         for b, (n, c) in enumerate(step):
             got[n][at[n]:at[n] + c] = o[cu[b]:cu[b + 1]]
             at[n] += c
@@ -318,7 +320,29 @@ def test_delta_rule_overwrites_what_a_key_held(ctx, ops):
     x[T - 1, 0] = big                            # the last token reads key axis 0
     conv_w = torch.ones(2 * d + vd, 1)           # one tap: the convolution passes its input through
     state, cstate = torch.zeros(1, H, d, vd, device=DEV), torch.zeros(1, 1, 2 * d + vd, device=DEV)
-    o, q, k, v, gb = ops.delta_rule(ctx, x.to(DEV), (0, d, 2 * d, 2 * d + vd, 2 * d + vd + 1), H, 1, d, vd, 1, conv_w.to(DEV), cstate, state, i32([0]),
-                                    i32([0, T]), i32(list(range(T))), torch.zeros(1, device=DEV), torch.zeros(1, device=DEV))
     v5 = torch.nn.functional.silu(x[5, 2 * d:2 * d + vd])
-    assert torch.allclose(o.cpu()[T - 1], v5 * d ** -0.5, rtol=1e-4, atol=1e-6)
+    for max_qlen in (1, T):
+        state, cstate = torch.zeros(1, H, d, vd, device=DEV), torch.zeros(1, 1, 2 * d + vd, device=DEV)
+        o, q, k, v, gb = ops.delta_rule(ctx, x.to(DEV), (0, d, 2 * d, 2 * d + vd, 2 * d + vd + 1), H, 1, d, vd, 1, conv_w.to(DEV), cstate, state, i32([0]),
+                                        i32([0, T]), i32(list(range(T))), torch.zeros(1, device=DEV), torch.zeros(1, device=DEV), max_qlen=max_qlen)
+        assert torch.allclose(o.cpu()[T - 1], v5 * d ** -0.5, rtol=1e-4, atol=1e-6)
+
+
+def test_a_decay_that_underflows_inside_a_chunk(ctx, ops):
+    """Strong decays (g around e^-30 per token): over a 32-token chunk their product is far below the smallest float.  The chunked
+    form exponentiates only differences of running log sums, so it stays finite and agrees with the token-by-token form."""
+    g = torch.Generator().manual_seed(16)
+    H, d, vd, T = 2, 16, 16, 70
+    ld = 2 * d + H * vd + 2 * H
+    x = torch.randn(T, ld, generator=g)
+    x[:, 2 * d + H * vd + H:] += 3.0                 # large softplus arguments
+    conv_w = torch.ones(2 * d + H * vd, 1)
+    A_log = torch.tensor([2.3, -1.0])                # exp(2.3) ~ 10 per unit of softplus for head 0
+    outs = []
+    for max_qlen in (1, T):
+        state, cstate = torch.zeros(1, H, d, vd, device=DEV), torch.zeros(1, 1, 2 * d + H * vd, device=DEV)
+        o = ops.delta_rule(ctx, x.to(DEV), (0, d, 2 * d, 2 * d + H * vd, 2 * d + H * vd + H), H, 1, d, vd, 1, conv_w.to(DEV), cstate, state, i32([0]),
+                           i32([0, T]), i32(list(range(T))), A_log.to(DEV), torch.zeros(H, device=DEV), max_qlen=max_qlen)[0].cpu()
+        assert torch.isfinite(o).all()
+        outs.append(o)
+    assert torch.allclose(outs[0], outs[1], rtol=1e-4, atol=1e-6)
