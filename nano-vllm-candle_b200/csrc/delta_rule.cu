@@ -212,14 +212,24 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
 // padded with g = 1, beta = 0, k = q = v = 0, which leaves state and outputs alone.
 constexpr int kDC = 32;
 constexpr int kDW = 4;
+constexpr int kDAs = kDC + 4;            // row stride of the token-by-token matrices (16-byte rows)
 
-__host__ __device__ inline size_t delta_chunk_smem_floats(int dim) {
-  return (size_t)2 * kDC * (dim + 1) + 2 * kDC * (kDC + 1) + 3 * kDC * 32 + (size_t)kDW * kDC * 32 + 2 * kDC + 8;
+// staged key / query rows: 4 DPT numbers and more (zeros behind `dim`), 16-byte aligned, rows 4 banks apart
+__host__ __device__ inline int delta_chunk_row(int dim, int dpt) { return max((dim + 3) / 4 * 4, kDW * dpt) + 4; }
+__host__ __device__ inline size_t delta_chunk_smem_floats(int dim, int dpt) {
+  return (size_t)2 * kDC * delta_chunk_row(dim, dpt) + 2 * kDC * kDAs + 3 * kDC * 32 + (size_t)kDW * kDC * 32 + 2 * kDC + 8;
+}
+
+__device__ __forceinline__ float fma4(const float4& x, const float4& y, float acc) {
+  acc = fmaf(x.x, y.x, acc);
+  acc = fmaf(x.y, y.y, acc);
+  acc = fmaf(x.z, y.z, acc);
+  return fmaf(x.w, y.w, acc);
 }
 
 template <int DPT>
 __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const nvc_delta_prep& p = a.p;
   const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
@@ -227,7 +237,8 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
   const int v = v0 + lane;
   const bool vok = v < p.vdim;
   const int hk = h / (p.heads / p.kv_heads);
-  const int dim = p.dim, ds = dim + 1, as = kDC + 1;
+  const int dim = p.dim, ds = delta_chunk_row(dim, DPT), dz = ds - 4;      // dz: numbers of a row that the products read
+  constexpr int as = kDAs;
   float* Ks = sm;                          // [kDC][ds]
   float* Qs = Ks + kDC * ds;               // [kDC][ds]
   float* Am = Qs + kDC * ds;               // [kDC][as]  beta_t exp(L_t - L_j) (k_t . k_j), j < t
@@ -245,19 +256,23 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
   const int slot = p.state_slots[b];
   advance_conv_state(p, r0, r1, fresh, slot);
   const int d0 = w * DPT;
-  float S[DPT];
+  float S[DPT];                            // rows behind `dim` stay zero: the staged rows are zero there
   float* sp = a.state + (((int64_t)slot * p.heads + h) * dim) * p.vdim;
 #pragma unroll
   for (int i = 0; i < DPT; ++i) S[i] = (!fresh && vok && d0 + i < dim) ? sp[(int64_t)(d0 + i) * p.vdim + v] : 0.f;
   for (int c0 = r0; c0 < r1; c0 += kDC) {
     const int n = min(kDC, r1 - c0);
-    // ---- stage the chunk
-    for (int idx = threadIdx.x; idx < kDC * dim; idx += kDW * 32) {
-      const int t = idx / dim, c = idx - t * dim;
-      Ks[t * ds + c] = t < n ? p.k_out[(int64_t)(c0 + t) * p.ldk + hk * dim + c] : 0.f;
-      Qs[t * ds + c] = t < n ? p.q_out[(int64_t)(c0 + t) * p.ldq + hk * dim + c] : 0.f;
+    // ---- stage the chunk (a row per warp and pass: no division, coalesced)
+    for (int t = w; t < kDC; t += kDW) {
+      const float* kg = p.k_out + (int64_t)(c0 + t) * p.ldk + hk * dim;
+      const float* qg = p.q_out + (int64_t)(c0 + t) * p.ldq + hk * dim;
+      for (int c = lane; c < dz; c += 32) {
+        const bool in = t < n && c < dim;
+        Ks[t * ds + c] = in ? kg[c] : 0.f;
+        Qs[t * ds + c] = in ? qg[c] : 0.f;
+      }
+      Us[t * 32 + lane] = (t < n && vok) ? p.v_out[(int64_t)(c0 + t) * p.ldv + h * p.vdim + v] : 0.f;
     }
-    for (int t = w; t < kDC; t += kDW) Us[t * 32 + lane] = (t < n && vok) ? p.v_out[(int64_t)(c0 + t) * p.ldv + h * p.vdim + v] : 0.f;
     if (w == 0) {
       float lg = lane < n ? p.gb_out[(int64_t)(c0 + lane) * 2 * p.heads + 2 * h] : 0.f;
 #pragma unroll
@@ -269,25 +284,33 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
       Bs[lane] = lane < n ? p.gb_out[(int64_t)(c0 + lane) * 2 * p.heads + 2 * h + 1] : 0.f;
     }
     __syncthreads();
-    // ---- products between the chunk's tokens (row t per warp, column j per lane)
-    for (int t = w; t < kDC; t += kDW) {
-      float kk = 0.f, qk = 0.f;
-      if (lane <= t) {
-        const float* kt = Ks + t * ds;
-        const float* qt = Qs + t * ds;
-        const float* kj = Ks + lane * ds;
-#pragma unroll 4
-        for (int c = 0; c < dim; ++c) {
-          const float x = kj[c];
-          kk = fmaf(kt[c], x, kk);
-          qk = fmaf(qt[c], x, qk);
+    // ---- products between the chunk's tokens: two rows t per warp and pass, column j per lane, 16-byte operands
+    for (int t = 2 * w; t < kDC; t += 2 * kDW) {
+      float kk0 = 0.f, qk0 = 0.f, kk1 = 0.f, qk1 = 0.f;
+      if (lane <= t + 1) {
+        const float4* kt0 = reinterpret_cast<const float4*>(Ks + t * ds);
+        const float4* qt0 = reinterpret_cast<const float4*>(Qs + t * ds);
+        const float4* kt1 = reinterpret_cast<const float4*>(Ks + (t + 1) * ds);
+        const float4* qt1 = reinterpret_cast<const float4*>(Qs + (t + 1) * ds);
+        const float4* kj = reinterpret_cast<const float4*>(Ks + lane * ds);
+#pragma unroll 2
+        for (int c = 0; c < dz / 4; ++c) {
+          const float4 x = kj[c];
+          kk0 = fma4(kt0[c], x, kk0);
+          qk0 = fma4(qt0[c], x, qk0);
+          kk1 = fma4(kt1[c], x, kk1);
+          qk1 = fma4(qt1[c], x, qk1);
         }
-        const float e = expf(Ls[t] - Ls[lane]);
-        kk *= e * Bs[t];
-        qk *= e;
+        const float e0 = expf(fminf(Ls[t] - Ls[lane], 0.f)), e1 = expf(fminf(Ls[t + 1] - Ls[lane], 0.f));
+        kk0 *= e0 * Bs[t];
+        qk0 *= e0;
+        kk1 *= e1 * Bs[t + 1];
+        qk1 *= e1;
       }
-      Am[t * as + lane] = lane < t ? kk : 0.f;
-      Pm[t * as + lane] = lane <= t ? qk : 0.f;
+      Am[t * as + lane] = lane < t ? kk0 : 0.f;
+      Pm[t * as + lane] = lane <= t ? qk0 : 0.f;
+      Am[(t + 1) * as + lane] = lane < t + 1 ? kk1 : 0.f;
+      Pm[(t + 1) * as + lane] = lane <= t + 1 ? qk1 : 0.f;
     }
     // ---- what the state before the chunk says to every key and query: partial sums over this warp's rows, then over the warps
 #pragma unroll 1
@@ -300,10 +323,14 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
 #pragma unroll
         for (int u = 0; u < 8; ++u) acc[u] = 0.f;
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-          if (d0 + i < dim) {
+        for (int i = 0; i < DPT; i += 4) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) acc[u] = fmaf(S[i], X[(t0 + u) * ds + d0 + i], acc[u]);
+          for (int u = 0; u < 8; ++u) {
+            const float4 x = *reinterpret_cast<const float4*>(X + (t0 + u) * ds + d0 + i);
+            acc[u] = fmaf(S[i], x.x, acc[u]);
+            acc[u] = fmaf(S[i + 1], x.y, acc[u]);
+            acc[u] = fmaf(S[i + 2], x.z, acc[u]);
+            acc[u] = fmaf(S[i + 3], x.w, acc[u]);
           }
         }
 #pragma unroll
@@ -325,34 +352,52 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
       for (int t = 0; t < kDC; ++t) {
         float x = Bs[t] * (Us[t * 32 + lane] - expf(Ls[t]) * W1[t * 32 + lane]);
 #pragma unroll
-        for (int j = 0; j < t; ++j) x = fmaf(-Am[t * as + j], u[j], x);
+        for (int j4 = 0; j4 < t; j4 += 4) {       // entries at and behind the diagonal are zero
+          const float4 am = *reinterpret_cast<const float4*>(Am + t * as + j4);
+          x = fmaf(-am.x, u[j4], x);
+          if (j4 + 1 < t) x = fmaf(-am.y, u[j4 + 1], x);
+          if (j4 + 2 < t) x = fmaf(-am.z, u[j4 + 2], x);
+          if (j4 + 3 < t) x = fmaf(-am.w, u[j4 + 3], x);
+        }
         u[t] = x;
       }
 #pragma unroll
       for (int t = 0; t < kDC; ++t) Us[t * 32 + lane] = u[t];
     }
     __syncthreads();
-    // ---- outputs
-    for (int t = w; t < n; t += kDW) {
-      float o = expf(Ls[t]) * W2[t * 32 + lane];
-      for (int j = 0; j <= t; ++j) o = fmaf(Pm[t * as + j], Us[j * 32 + lane], o);
-      if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * p.vdim + v] = o;
-    }
-    // ---- the state behind the chunk
+    // ---- outputs and the state behind the chunk
     {
-      const float Ln = Ls[kDC - 1];
-      const float gn = expf(Ln);
       float uu[kDC];
 #pragma unroll
-      for (int j = 0; j < kDC; ++j) uu[j] = expf(Ln - Ls[j]) * Us[j * 32 + lane];
+      for (int j = 0; j < kDC; ++j) uu[j] = Us[j * 32 + lane];
+      for (int t = w; t < n; t += kDW) {
+        float o = expf(Ls[t]) * W2[t * 32 + lane];
 #pragma unroll
-      for (int i = 0; i < DPT; ++i) {
-        if (d0 + i < dim) {
-          float s = gn * S[i];
-#pragma unroll
-          for (int j = 0; j < kDC; ++j) s = fmaf(Ks[j * ds + d0 + i], uu[j], s);
-          S[i] = s;
+        for (int j4 = 0; j4 < kDC; j4 += 4) {     // entries behind the diagonal are zero
+          const float4 pm = *reinterpret_cast<const float4*>(Pm + t * as + j4);
+          o = fmaf(pm.x, uu[j4], o);
+          o = fmaf(pm.y, uu[j4 + 1], o);
+          o = fmaf(pm.z, uu[j4 + 2], o);
+          o = fmaf(pm.w, uu[j4 + 3], o);
         }
+        if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * p.vdim + v] = o;
+      }
+      const float Ln = Ls[kDC - 1];
+      const float gn = expf(Ln);
+#pragma unroll
+      for (int j = 0; j < kDC; ++j) uu[j] *= expf(Ln - Ls[j]);
+#pragma unroll
+      for (int i = 0; i < DPT; i += 4) {
+        float s0 = gn * S[i], s1 = gn * S[i + 1], s2 = gn * S[i + 2], s3 = gn * S[i + 3];
+#pragma unroll
+        for (int j = 0; j < kDC; ++j) {
+          const float4 x = *reinterpret_cast<const float4*>(Ks + j * ds + d0 + i);
+          s0 = fmaf(x.x, uu[j], s0);
+          s1 = fmaf(x.y, uu[j], s1);
+          s2 = fmaf(x.z, uu[j], s2);
+          s3 = fmaf(x.w, uu[j], s3);
+        }
+        S[i] = s0; S[i + 1] = s1; S[i + 2] = s2; S[i + 3] = s3;
       }
     }
     __syncthreads();
@@ -403,16 +448,17 @@ extern "C" int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float*
   NVC_REQUIRE(ctx, o && state && ldo >= p->heads * p->vdim && max_qlen >= 1, NVC_EINVAL, "bad output / state");
   DeltaArgs a{*p, 0, o, ldo, state};
   const int dim = p->dim;
-  if (p->cu_seqlens && max_qlen >= 8 && dim <= 512 && delta_chunk_smem_floats(dim) * sizeof(float) <= 200 * 1024) {
+  if (p->cu_seqlens && max_qlen >= 8 && dim <= 512) {
     // prompt portions: 32 tokens at a time
     const int per = (dim + kDW - 1) / kDW;     // rows of the state per warp
+    const int cd = per <= 8 ? 8 : (per <= 16 ? 16 : (per <= 32 ? 32 : (per <= 64 ? 64 : 128)));
     const dim3 grid(p->B, p->heads, (p->vdim + 31) / 32);
-    const size_t smem = delta_chunk_smem_floats(dim) * sizeof(float);
+    const size_t smem = delta_chunk_smem_floats(dim, cd) * sizeof(float);
     cudaError_t ce;
-    if (per <= 8) ce = launch_delta_chunk<8>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (per <= 16) ce = launch_delta_chunk<16>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (per <= 32) ce = launch_delta_chunk<32>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (per <= 64) ce = launch_delta_chunk<64>(ctx, a, grid, smem, nvc_stream(stream));
+    if (cd == 8) ce = launch_delta_chunk<8>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (cd == 16) ce = launch_delta_chunk<16>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (cd == 32) ce = launch_delta_chunk<32>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (cd == 64) ce = launch_delta_chunk<64>(ctx, a, grid, smem, nvc_stream(stream));
     else ce = launch_delta_chunk<128>(ctx, a, grid, smem, nvc_stream(stream));
     NVC_CUDA_CHECK(ctx, ce);
     ctx->launches++;

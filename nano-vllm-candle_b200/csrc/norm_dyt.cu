@@ -86,29 +86,46 @@ __global__ void latent_norm_store_kernel(const float* __restrict__ in, int ldi, 
 
 // NVC_ACT_GELU_TANH_MUL: out[n, j] = gelu_tanh(in[n, j]) * in[n, Fp + j];  NVC_ACT_RELU2: out[n, j] = relu(in[n, j])^2;
 // NVC_ACT_GELU_TANH: gelu_tanh(in[n, j]);  NVC_ACT_GLU_CLAMP: g sigmoid(p1 g) (u + 1), g = min(in[n, j], p0), u = clamp(in[n, Fp + j], +-p0)
-template <typename T>
+__device__ __forceinline__ float act_unit(int kind, float g, float u, float p0, float p1) {
+  if (kind == NVC_ACT_GELU_TANH_MUL) return gelu_tanh_f32(g) * u;
+  if (kind == NVC_ACT_GELU_TANH) return gelu_tanh_f32(g);
+  if (kind == NVC_ACT_GLU_CLAMP) {
+    const float gc = fminf(g, p0);
+    return gc * sigmoid_f32(p1 * gc) * (fminf(fmaxf(u, -p0), p0) + 1.0f);
+  }
+  const float t = fmaxf(g, 0.f);
+  return t * t;
+}
+
+// rows_per_cta rows per CTA, the threads walk along a row: no division per element.  V: numbers per access (8 when every
+// row start is 16-byte aligned in both buffers and F, Fp are multiples of 8; else 1)
+template <typename T, int V>
 __global__ void act_mul_kernel(const T* __restrict__ in, int ldi, T* __restrict__ out, int ldo, int N, int F, int Fp, int kind, float p0,
-                               float p1) {
+                               float p1, int rows_per_cta) {
   pdl_trigger();
   pdl_wait();
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (int64_t)N * F) return;
-  const int n = (int)(i / F), j = (int)(i % F);
-  const float g = ld_f(in + (int64_t)n * ldi + j);
-  float y;
-  if (kind == NVC_ACT_GELU_TANH_MUL) {
-    y = gelu_tanh_f32(g) * ld_f(in + (int64_t)n * ldi + Fp + j);
-  } else if (kind == NVC_ACT_GELU_TANH) {
-    y = gelu_tanh_f32(g);
-  } else if (kind == NVC_ACT_GLU_CLAMP) {
-    const float gc = fminf(g, p0);
-    const float u = fminf(fmaxf(ld_f(in + (int64_t)n * ldi + Fp + j), -p0), p0);
-    y = gc * sigmoid_f32(p1 * gc) * (u + 1.0f);
-  } else {
-    const float t = fmaxf(g, 0.f);
-    y = t * t;
+  const bool two = kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_GLU_CLAMP;
+  for (int rr = 0; rr < rows_per_cta; ++rr) {
+    const int64_t n = (int64_t)blockIdx.x * rows_per_cta + rr;
+    if (n >= N) return;
+    const T* x = in + n * ldi;
+    T* y = out + n * ldo;
+    if constexpr (V == 1) {
+      for (int j = threadIdx.x; j < F; j += blockDim.x) st_f(y + j, act_unit(kind, ld_f(x + j), two ? ld_f(x + Fp + j) : 0.f, p0, p1));
+    } else {
+      constexpr int PER = 16 / sizeof(T);          // numbers per 16-byte access
+      for (int j = threadIdx.x * PER; j < F; j += blockDim.x * PER) {
+        __align__(16) T g[PER];
+        __align__(16) T u[PER];
+        __align__(16) T o[PER];
+        *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(x + j);
+        if (two) *reinterpret_cast<uint4*>(u) = *reinterpret_cast<const uint4*>(x + Fp + j);
+#pragma unroll
+        for (int k = 0; k < PER; ++k) st_f(o + k, act_unit(kind, ld_f(g + k), two ? ld_f(u + k) : 0.f, p0, p1));
+        *reinterpret_cast<uint4*>(y + j) = *reinterpret_cast<const uint4*>(o);
+      }
+    }
   }
-  st_f(out + (int64_t)n * ldo + j, y);
 }
 
 }  // namespace
@@ -184,11 +201,19 @@ int nvc_act_mul_p(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int
   NVC_REQUIRE(ctx, N >= 0 && F > 0 && (two || kind == NVC_ACT_RELU2 || kind == NVC_ACT_GELU_TANH), NVC_EINVAL, "bad arguments");
   NVC_REQUIRE(ctx, ldo >= F && ldi >= (two ? Fp + F : F), NVC_EINVAL, "bad strides");
   if (N == 0) return NVC_OK;
-  const int64_t total = (int64_t)N * F;
-  NVC_DISPATCH_DT(dtype, T,
-                  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, act_mul_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
-                                                 nvc_stream(stream), reinterpret_cast<const T*>(in), ldi, reinterpret_cast<T*>(out), ldo,
-                                                 N, F, Fp, kind, p0, p1)));
+  const int per = dtype == NVC_DT_F32 ? 4 : 8;
+  const bool vec = F % per == 0 && Fp % per == 0 && ldi % per == 0 && ldo % per == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const int lanes = vec ? F / per : F;                       // accesses per row
+  const int threads = lanes >= 256 ? 256 : (lanes >= 128 ? 128 : 64);
+  const int rows_per_cta = lanes >= 64 ? 1 : (64 / (lanes > 0 ? lanes : 1));
+  const unsigned grid = (unsigned)((N + rows_per_cta - 1) / rows_per_cta);
+  NVC_DISPATCH_DT(dtype, T, {
+    auto k1 = act_mul_kernel<T, 1>;
+    auto k8 = act_mul_kernel<T, 8>;
+    NVC_CUDA_CHECK(ctx, nvc_launch(ctx, vec ? k8 : k1, dim3(grid), dim3(threads), 0, nvc_stream(stream), reinterpret_cast<const T*>(in), ldi,
+                                   reinterpret_cast<T*>(out), ldo, N, F, Fp, kind, p0, p1, rows_per_cta));
+  });
   ctx->launches++;
   return NVC_OK;
 }

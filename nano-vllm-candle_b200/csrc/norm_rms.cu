@@ -114,10 +114,92 @@ __global__ void rms_norm_sandwich_kernel(const float* __restrict__ res_in, const
   for (int j = threadIdx.x; j < H; j += blockDim.x) st_f(out + (int64_t)blockIdx.x * ldo + j, row[j] * r * (__ldg(w + j) + woff));
 }
 
-// one warp per (row, head)
+// the same with rows of 4 V numbers per thread kept in registers and 16-byte accesses (H a multiple of 4, H <= 4 V blockDim.x)
+__device__ __forceinline__ void st4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float4& v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ float block_sum(float v, float* part) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+  if (threadIdx.x < 32) {
+    t = warp_sum(t);
+    if (threadIdx.x == 0) part[32] = t;
+  }
+  __syncthreads();
+  t = part[32];
+  __syncthreads();
+  return t;
+}
+
+template <typename T, int V>
+__global__ void rms_norm_sandwich_vec_kernel(const float* __restrict__ res_in, const float* __restrict__ y, const float* __restrict__ wy,
+                                             float* __restrict__ res_out, int ld, const float* __restrict__ w, T* __restrict__ out, int ldo,
+                                             float eps, float woff, const int32_t* __restrict__ rows, int H) {
+  __shared__ float part[33];
+  pdl_trigger();
+  pdl_wait();
+  const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+  const int H4 = H >> 2;
+  float4 s[V];
+  float4 yy[V];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int j = threadIdx.x + k * blockDim.x;
+    s[k] = j < H4 ? *reinterpret_cast<const float4*>(res_in + src * ld + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (y) {
+      yy[k] = j < H4 ? *reinterpret_cast<const float4*>(y + src * ld + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      ss += yy[k].x * yy[k].x + yy[k].y * yy[k].y + yy[k].z * yy[k].z + yy[k].w * yy[k].w;
+    }
+  }
+  if (y) {
+    const float ry = 1.0f / sqrtf(block_sum(ss, part) / (float)H + eps);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const int j = threadIdx.x + k * blockDim.x;
+      if (j < H4) {
+        const float4 g = *reinterpret_cast<const float4*>(wy + 4 * j);
+        s[k].x += yy[k].x * ry * (g.x + woff);
+        s[k].y += yy[k].y * ry * (g.y + woff);
+        s[k].z += yy[k].z * ry * (g.z + woff);
+        s[k].w += yy[k].w * ry * (g.w + woff);
+      }
+    }
+  }
+  ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int j = threadIdx.x + k * blockDim.x;
+    if (j < H4) {
+      if (res_out) *reinterpret_cast<float4*>(res_out + src * ld + 4 * j) = s[k];
+      ss += s[k].x * s[k].x + s[k].y * s[k].y + s[k].z * s[k].z + s[k].w * s[k].w;
+    }
+  }
+  if (!w) return;
+  const float r = 1.0f / sqrtf(block_sum(ss, part) / (float)H + eps);
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int j = threadIdx.x + k * blockDim.x;
+    if (j < H4) {
+      const float4 g = *reinterpret_cast<const float4*>(w + 4 * j);
+      st4(out + (int64_t)blockIdx.x * ldo + 4 * j,
+          make_float4(s[k].x * r * (g.x + woff), s[k].y * r * (g.y + woff), s[k].z * r * (g.z + woff), s[k].w * r * (g.w + woff)));
+    }
+  }
+}
+
+// one warp per (row, head); vec: vdim and every stride are multiples of 4 and the pointers 16-byte aligned (16-byte accesses)
 template <typename T>
 __global__ void head_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg,
-                                 const float* __restrict__ wgt, T* __restrict__ out, int ldout, int heads, int vdim, int norm, float eps, int act, float out_scale, int N) {
+                                 const float* __restrict__ wgt, T* __restrict__ out, int ldout, int heads, int vdim, int norm, float eps, int act,
+                                 float out_scale, int N, int vec) {
   pdl_trigger();
   pdl_wait();
   const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -125,6 +207,37 @@ __global__ void head_gate_kernel(const float* __restrict__ o, int ldo, const flo
   if (u >= (int64_t)N * heads) return;
   const int n = (int)(u / heads), h = (int)(u % heads);
   const float* x = o + (int64_t)n * ldo + (int64_t)h * vdim;
+  const float* z = g ? g + (int64_t)n * ldg + (int64_t)h * vdim : nullptr;
+  T* dst = out + (int64_t)n * ldout + (int64_t)h * vdim;
+  if (vec) {
+    const int v4 = vdim >> 2;
+    float r = 1.f;
+    if (norm) {
+      float ss = 0.f;
+      for (int j = lane; j < v4; j += 32) {
+        const float4 a = *reinterpret_cast<const float4*>(x + 4 * j);
+        ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      }
+      ss = warp_sum(ss);
+      r = 1.0f / sqrtf(ss / (float)vdim + eps);
+    }
+    r *= out_scale;
+    for (int j = lane; j < v4; j += 32) {
+      float4 a = *reinterpret_cast<const float4*>(x + 4 * j);
+      a.x *= r; a.y *= r; a.z *= r; a.w *= r;
+      if (wgt) {
+        const float4 c = *reinterpret_cast<const float4*>(wgt + 4 * j);
+        a.x *= c.x; a.y *= c.y; a.z *= c.z; a.w *= c.w;
+      }
+      if (z) {
+        const float4 c = *reinterpret_cast<const float4*>(z + 4 * j);
+        if (act == NVC_GATE_SILU) { a.x *= c.x * sigmoid_f32(c.x); a.y *= c.y * sigmoid_f32(c.y); a.z *= c.z * sigmoid_f32(c.z); a.w *= c.w * sigmoid_f32(c.w); }
+        else { a.x *= sigmoid_f32(c.x); a.y *= sigmoid_f32(c.y); a.z *= sigmoid_f32(c.z); a.w *= sigmoid_f32(c.w); }
+      }
+      st4(dst + 4 * j, a);
+    }
+    return;
+  }
   float r = 1.f;
   if (norm) {
     float ss = 0.f;
@@ -135,11 +248,8 @@ __global__ void head_gate_kernel(const float* __restrict__ o, int ldo, const flo
   for (int j = lane; j < vdim; j += 32) {
     float y = x[j] * r;
     if (wgt) y *= __ldg(wgt + j);
-    if (g) {
-      const float z = g[(int64_t)n * ldg + (int64_t)h * vdim + j];
-      y *= act == NVC_GATE_SILU ? z * sigmoid_f32(z) : sigmoid_f32(z);
-    }
-    st_f(out + (int64_t)n * ldout + (int64_t)h * vdim + j, y * out_scale);
+    if (z) y *= act == NVC_GATE_SILU ? z[j] * sigmoid_f32(z[j]) : sigmoid_f32(z[j]);
+    st_f(dst + j, y * out_scale);
   }
 }
 
@@ -187,6 +297,22 @@ int nvc_rms_norm_sandwich(nvc_ctx* ctx, const float* res_in, const float* y, con
   NVC_REQUIRE(ctx, N >= 0 && H > 0 && H <= 12288 && ld >= H && (!w || ldo >= H), NVC_EINVAL, "bad sizes (rows of up to 12 288 numbers)");
   NVC_REQUIRE(ctx, !(rows && res_out), NVC_EINVAL, "a gathering call does not write the residual back");
   if (N == 0) return NVC_OK;
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (H % 4 == 0 && ld % 4 == 0 && (!w || ldo % 4 == 0) && H <= 8192 && al16(res_in) && al16(y) && al16(wy) && al16(res_out) && al16(w) && al16(out)) {
+    // rows in registers, 16-byte accesses: one float4 per thread up to 1024 numbers, two up to 4096 (256 and 512 threads), then four
+    const int H4 = H / 4;
+    const int threads = H4 <= 64 ? 64 : (H4 <= 128 ? 128 : (H4 <= 256 ? 256 : 512));
+    const int V = (H4 + threads - 1) / threads;
+    NVC_DISPATCH_DT(out_dtype, T, {
+      auto k1 = rms_norm_sandwich_vec_kernel<T, 1>;
+      auto k2 = rms_norm_sandwich_vec_kernel<T, 2>;
+      auto k4 = rms_norm_sandwich_vec_kernel<T, 4>;
+      NVC_CUDA_CHECK(ctx, nvc_launch(ctx, V <= 1 ? k1 : (V <= 2 ? k2 : k4), dim3(N), dim3(threads), 0, nvc_stream(stream), res_in, y, wy, res_out, ld, w,
+                                     reinterpret_cast<T*>(out), ldo, eps, weight_offset, rows, H));
+    });
+    ctx->launches++;
+    return NVC_OK;
+  }
   const int threads = H >= 1024 ? 512 : (H >= 256 ? 256 : 128);
   NVC_DISPATCH_DT(out_dtype, T,
                   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, rms_norm_sandwich_kernel<T>, dim3(N), dim3(threads), (size_t)H * sizeof(float),
@@ -209,10 +335,12 @@ int nvc_head_gate_w(nvc_ctx* ctx, const float* o, int ldo, const float* gate, in
   NVC_REQUIRE(ctx, act == NVC_GATE_SIGMOID || act == NVC_GATE_SILU, NVC_EINVAL, "unknown gate");
   if (N == 0) return NVC_OK;
   const int64_t units = (int64_t)N * heads;
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const int vec = vdim % 4 == 0 && ldo % 4 == 0 && ldout % 4 == 0 && (!gate || ldg % 4 == 0) && al16(o) && al16(gate) && al16(weight) && al16(out);
   NVC_DISPATCH_DT(out_dtype, T,
                   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, head_gate_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0,
                                                  nvc_stream(stream), o, ldo, gate, ldg, weight, reinterpret_cast<T*>(out), ldout, heads, vdim, norm,
-                                                 eps, act, out_scale, N)));
+                                                 eps, act, out_scale, N, vec)));
   ctx->launches++;
   return NVC_OK;
 }

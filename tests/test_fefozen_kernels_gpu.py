@@ -28,7 +28,7 @@ def i32(x):
 
 # ------------------------------------------------------------------------------------------ norms
 @pytest.mark.parametrize("dt", DTS)
-@pytest.mark.parametrize("H", [24, 200, 1100])
+@pytest.mark.parametrize("H", [24, 37, 200, 1100, 5000])
 def test_norm_behind_and_in_front_of_a_sublayer(ctx, ops, dt, H):
     g = torch.Generator().manual_seed(2)
     N, eps = 7, 1e-3
@@ -156,7 +156,11 @@ def test_head_norm_with_a_shared_weight_and_a_silu_gate(ctx, ops, dt):
 @pytest.mark.parametrize("dt", DTS)
 def test_clamped_gated_unit_and_plain_gelu(ctx, ops, dt):
     g = torch.Generator().manual_seed(7)
-    N, Fn, Fp = 13, 37, 40
+    run_gated_units(ctx, ops, dt, g, 13, 37, 40)
+    run_gated_units(ctx, ops, dt, g, 70, 96, 128)          # rows that take 16-byte accesses
+
+
+def run_gated_units(ctx, ops, dt, g, N, Fn, Fp):
     x = (torch.randn(N, 2 * Fp, generator=g) * 2).to(dt)
     xf = x.float()
     for limit in (1.0, 0.25, 7.0):
