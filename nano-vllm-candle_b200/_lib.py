@@ -115,6 +115,7 @@ def _declare(l: C.CDLL) -> None:
         "nvc_qkv_prep_run": [_vp, _vp, _i, _vp],
         "nvc_attn_paged_wide": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp],
         "nvc_retention_scan": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "nvc_prefill_attn_paged_sink": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _i, _vp],
         "nvc_rms_norm_sandwich": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _f, _vp, _i, _i, _vp],
         "nvc_latent_norm_store_rot": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp],
         "nvc_head_split_rot": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp],

@@ -21,6 +21,7 @@ namespace {
 struct DeltaArgs {
   nvc_delta_prep p;
   int N;
+  int vec;                       // sizes, strides and pointers allow 16-byte accesses
   float* o;
   int ldo;
   float* state;
@@ -75,6 +76,40 @@ __global__ void delta_prep_kernel(const DeltaArgs a) {
   const int ch = (kind == 0 ? 0 : (kind == 1 ? p.kv_heads * p.dim : 2 * p.kv_heads * p.dim)) + h * width;   // channel
   float* out = kind == 0 ? p.q_out + (int64_t)n * p.ldq : (kind == 1 ? p.k_out + (int64_t)n * p.ldk : p.v_out + (int64_t)n * p.ldv);
   out += h * width;
+  if (a.vec && width <= 512) {
+    // four channels per lane, 16-byte accesses, the head stays in registers between the convolution and the unit length
+    float4 y[4];
+    float ss4 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = 4 * lane + 128 * k;
+      y[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < width) {
+        const float* w = p.conv_w + (int64_t)(ch + j) * p.taps;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < p.taps; ++i) {
+          const int src = t - (p.taps - 1) + i;
+          float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (src >= 0) x = *reinterpret_cast<const float4*>(in + (int64_t)(src - t) * p.ldi + col + j);
+          else if (!fresh) x = *reinterpret_cast<const float4*>(cs + (int64_t)(p.taps - 1 + src) * C + ch + j);
+          acc.x = fmaf(__ldg(w + i), x.x, acc.x);
+          acc.y = fmaf(__ldg(w + p.taps + i), x.y, acc.y);
+          acc.z = fmaf(__ldg(w + 2 * p.taps + i), x.z, acc.z);
+          acc.w = fmaf(__ldg(w + 3 * p.taps + i), x.w, acc.w);
+        }
+        y[k] = make_float4(acc.x * sigmoid_f32(acc.x), acc.y * sigmoid_f32(acc.y), acc.z * sigmoid_f32(acc.z), acc.w * sigmoid_f32(acc.w));
+        ss4 += y[k].x * y[k].x + y[k].y * y[k].y + y[k].z * y[k].z + y[k].w * y[k].w;
+      }
+    }
+    float r = 1.f;
+    if (kind != 2) r = (kind == 0 ? p.q_scale : 1.f) / sqrtf(warp_sum(ss4) + p.unit_eps);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = 4 * lane + 128 * k;
+      if (j < width) *reinterpret_cast<float4*>(out + j) = make_float4(y[k].x * r, y[k].y * r, y[k].z * r, y[k].w * r);
+    }
+    return;
+  }
   float ss = 0.f;
   for (int j = lane; j < width; j += 32) {
     const float* w = p.conv_w + (int64_t)(ch + j) * p.taps;
@@ -435,7 +470,10 @@ extern "C" int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, 
   if (rc) return rc;
   NVC_REQUIRE(ctx, p->cu_seqlens || N == p->B, NVC_EINVAL, "rows without cu_seqlens: one per sequence");
   if (N == 0) return NVC_OK;
-  DeltaArgs a{*p, N, nullptr, 0, nullptr};
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const int vec = p->dim % 4 == 0 && p->vdim % 4 == 0 && p->ldi % 4 == 0 && p->q_off % 4 == 0 && p->k_off % 4 == 0 && p->v_off % 4 == 0 && p->ldq % 4 == 0 &&
+                  p->ldk % 4 == 0 && p->ldv % 4 == 0 && al16(p->in) && al16(p->conv_state) && al16(p->q_out) && al16(p->k_out) && al16(p->v_out);
+  DeltaArgs a{*p, N, vec, nullptr, 0, nullptr};
   const int64_t units = (int64_t)N * (2 * p->kv_heads + p->heads + 1);
   NVC_CUDA_CHECK(ctx, nvc_launch(ctx, delta_prep_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, nvc_stream(stream), a));
   ctx->launches++;
@@ -446,7 +484,7 @@ extern "C" int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float*
   int rc = check_prep(ctx, p);
   if (rc) return rc;
   NVC_REQUIRE(ctx, o && state && ldo >= p->heads * p->vdim && max_qlen >= 1, NVC_EINVAL, "bad output / state");
-  DeltaArgs a{*p, 0, o, ldo, state};
+  DeltaArgs a{*p, 0, 0, o, ldo, state};
   const int dim = p->dim;
   if (p->cu_seqlens && max_qlen >= 8 && dim <= 512) {
     // prompt portions: 32 tokens at a time

@@ -11,8 +11,8 @@
 //     attention               softmax over the cached rows: in the absorbed form a layer is multi-query attention with ONE key /
 //                             value head - key = the whole row (kv_rank + rot_dim numbers), value = its first kv_rank numbers.
 //                             nvc_attn_paged_wide (sink in its epilogue), or the tcgen05 paged-prefill kernel for long portions
-//                             when the row has 128 numbers and the layer has no sink (the rotated part rides along as value
-//                             columns that the value up-projection never reads)
+//                             when the row has 128 numbers (the sink joins the denominator in its epilogue; the rotated part
+//                             rides along as value columns that the value up-projection never reads)
 //     linear uv per head (fp32 out) -> nvc_head_gate (sigmoid gate of h) -> linear o
 //   delta:
 //     linear w_in             [q | k | v | beta | a | gate], fp32 out
@@ -390,7 +390,7 @@ struct FefozenBody : nvc_body_base {
   static constexpr int kFlashMinChunk = 64;
   bool flash_portions(const nvc_runner* r, const nvc_step_shape& s, const FLayerW& w, const nvc_latent_attn_spec& a) const {
     const int bs = r->opt.kvcache_block_size;
-    return use_flash && !a.sink && w.Dk == 128 && w.ldpool == 128 && !s.decode && s.num_decode < s.B && s.max_chunk >= kFlashMinChunk &&
+    return use_flash && w.Dk == 128 && w.ldpool == 128 && !s.decode && s.num_decode < s.B && s.max_chunk >= kFlashMinChunk &&
            (bs == 16 || bs == 32 || bs == 64 || bs % 128 == 0);
   }
 
@@ -440,9 +440,9 @@ struct FefozenBody : nvc_body_base {
       const nvc_bf16* qb = reinterpret_cast<const nvc_bf16*>(qabs);
       nvc_bf16* ob = reinterpret_cast<nvc_bf16*>(olat);
       const nvc_bf16* pb = reinterpret_cast<const nvc_bf16*>(pool);
-      if ((rc = nvc_prefill_attn_paged_ld(ctx, qb + (size_t)nd * w.ldqa, w.ldqa, pb, pb, r->d_bt + (size_t)nd * cap, cap, r->d_ctx + nd,
-                                          nd ? r->d_cu2 : r->d_cu, s.B - nd, s.N - nd, s.max_chunk, a.heads, 1, w.Dk, bs, r->opt.num_kvcache_blocks,
-                                          a.scale, ob + (size_t)nd * w.ldol, w.ldol, st)))
+      if ((rc = nvc_prefill_attn_paged_sink(ctx, qb + (size_t)nd * w.ldqa, w.ldqa, pb, pb, r->d_bt + (size_t)nd * cap, cap, r->d_ctx + nd,
+                                            nd ? r->d_cu2 : r->d_cu, s.B - nd, s.N - nd, s.max_chunk, a.heads, 1, w.Dk, bs, r->opt.num_kvcache_blocks,
+                                            a.scale, sp.sink, ob + (size_t)nd * w.ldol, w.ldol, st)))
         return rc;
     } else if ((rc = nvc_attn_paged_wide(ctx, qabs, w.ldqa, pool, w.ldpool, pool, w.ldpool, r->d_bt, cap, r->d_ctx, s.decode ? nullptr : r->d_cu, s.B,
                                          s.N, s.decode ? 1 : s.max_seqlen, bs, &sp, olat, w.ldol, dt, st))) {

@@ -41,6 +41,7 @@ struct PagedKV {                              // kPaged only
   int bt_stride;
   int block_size;
   int box_rows;                               // token rows per K / V TMA box = min(64, block_size)
+  const float* sink;                          // optional [nh]: one more term exp(sink_h) in every row's denominator, no value
 };
 
 int make_tma_heads(nvc_ctx* ctx, CUtensorMap* map, const void* base, int heads, int64_t tokens, int ld, int box_rows = 128) {
@@ -124,6 +125,15 @@ extern "C" int nvc_prefill_attn_paged_ld(nvc_ctx* ctx, const nvc_bf16* q, int ld
                                          const int32_t* context_lens, const int32_t* cu_seqlens_q, int B,
                                          int total_q_tokens, int max_seqlen_q, int nh, int kv, int hd, int block_size,
                                          int num_blocks, float scale, nvc_bf16* out, int ldo, void* stream) {
+  return nvc_prefill_attn_paged_sink(ctx, q, ldq, k_cache, v_cache, block_tables, bt_stride, context_lens, cu_seqlens_q, B, total_q_tokens,
+                                     max_seqlen_q, nh, kv, hd, block_size, num_blocks, scale, nullptr, out, ldo, stream);
+}
+
+extern "C" int nvc_prefill_attn_paged_sink(nvc_ctx* ctx, const nvc_bf16* q, int ldq, const nvc_bf16* k_cache,
+                                           const nvc_bf16* v_cache, const int32_t* block_tables, int bt_stride,
+                                           const int32_t* context_lens, const int32_t* cu_seqlens_q, int B,
+                                           int total_q_tokens, int max_seqlen_q, int nh, int kv, int hd, int block_size,
+                                           int num_blocks, float scale, const float* sink, nvc_bf16* out, int ldo, void* stream) {
   NVC_REQUIRE(ctx, ctx && ldo >= nh * hd && ldo % 8 == 0 && ((uintptr_t)out % 16) == 0, NVC_ESHAPE,
               "output rows must cover the heads, with a stride that is a multiple of 8 and a 16-byte aligned start");
   NVC_REQUIRE(ctx, ctx && q && k_cache && v_cache && block_tables && context_lens && cu_seqlens_q && out, NVC_EINVAL,
@@ -147,7 +157,7 @@ extern "C" int nvc_prefill_attn_paged_ld(nvc_ctx* ctx, const nvc_bf16* q, int ld
   if (rc) return rc;
   rc = make_tma_heads(ctx, &tv, v_cache, kv, (int64_t)num_blocks * block_size, kv * hd, box_rows);
   if (rc) return rc;
-  PagedKV pk{block_tables, context_lens, bt_stride, block_size, box_rows};
+  PagedKV pk{block_tables, context_lens, bt_stride, block_size, box_rows, sink};
   const int QT = (max_seqlen_q + 127) / 128;
   NVC_CUDA_CHECK(ctx, launch_v2<true>(ctx, QT, nh, kv, B, nvc_stream(stream), tq, tk, tv, cu_seqlens_q,
                                       scale * 1.4426950408889634f, out, ldo, pk));

@@ -387,6 +387,7 @@ prefill_attn_v2_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
       // ---- O / l -> bf16 rows of the output
       ptx::mbar_wait(o_full, (g + n - 1) & 1);
       ptx::tcgen05_fence_after();
+      if (kPaged && pk.sink) l += exp2f(__ldg(pk.sink + x.h) * 1.4426950408889634f - m);   // the sink: in the denominator, without a value
       const float inv = 1.0f / l;
       // this warp's 32 rows x 128 head dims leave through its staging buffer: 8 lanes per row, 128 contiguous bytes each
       RowStage st = make_row_stage(gen + kOffStage + quad * 4096, out, 0, NVC_EPI_NONE, (int64_t)ldo,

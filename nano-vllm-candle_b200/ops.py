@@ -267,6 +267,16 @@ class Context:
                  "nvc_prefill_attn_paged_ld")
         return out
 
+    def prefill_attn_paged_sink(self, q, k_cache, v_cache, block_tables, context_lens, cu_seqlens_q, max_seqlen_q,
+                                nh, kv, hd, block_size, scale, sink, out):
+        """The same with one more term exp(sink_h) in every row's softmax denominator (sink: fp32 [nh] or None)."""
+        N, B = q.shape[0], cu_seqlens_q.numel() - 1
+        self._ck(self.l.nvc_prefill_attn_paged_sink(self.h, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                                                    block_tables.shape[1], _ptr(context_lens), _ptr(cu_seqlens_q), B, N, max_seqlen_q, nh,
+                                                    kv, hd, block_size, k_cache.shape[0], float(scale), _ptr(sink), _ptr(out), out.stride(0),
+                                                    _stream()), "nvc_prefill_attn_paged_sink")
+        return out
+
     def paged_decode_attn(self, q, k_cache, v_cache, block_tables, context_lens, nh, kv, hd, block_size, scale, out=None):
         _req(q, BF16, "q"); _req(block_tables, torch.int32, "block_tables"); _req(context_lens, torch.int32, "context_lens")
         B = q.shape[0]

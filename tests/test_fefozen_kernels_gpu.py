@@ -142,6 +142,34 @@ def test_absorbed_attention_over_shared_rows(ctx, ops, dt, sink, R, rd, H):
             row += 1
 
 
+@pytest.mark.parametrize("sink", [False, True])
+def test_long_portions_over_128_number_rows_on_the_tensor_memory_kernel(ctx, ops, sink):
+    """The paged-prefill kernel of the dense families with key = value = the shared row and an optional sink, against the wide
+    kernel (checked above against plain softmax): portions of 64 tokens and more behind cached prefixes."""
+    g = torch.Generator().manual_seed(6)
+    bs, H, D = 16, 5, 128
+    ctxs, qls = [200, 70, 131], [129, 70, 64]
+    pool = torch.randn(40 * bs, D, generator=g).bfloat16().to(DEV)
+    perm = torch.randperm(40, generator=g)
+    bt = torch.zeros(3, 13, dtype=torch.int32)
+    at = 0
+    for b, c in enumerate(ctxs):
+        nb = (c + bs - 1) // bs
+        bt[b, :nb] = perm[at:at + nb]
+        at += nb
+    N = sum(qls)
+    q = (torch.randn(N, H * D, generator=g) * 0.5).bfloat16().to(DEV)
+    cu = i32([0, 129, 199, 263])
+    sk = torch.tensor([1.5, -1.0, 3.0, 0.0, 0.5]).to(DEV) if sink else None
+    want = ops.attn_paged_wide(ctx, q, pool, pool, bt.to(DEV), i32(ctxs), cu, 129, bs, H, 1, D, D, 0.09, sink=sk).float().cpu()
+    out = torch.zeros(N, H * D + 64, dtype=torch.bfloat16, device=DEV)
+    ctx.prefill_attn_paged_sink(q, pool.view(40, bs, 1, D), pool.view(40, bs, 1, D), bt.to(DEV), i32(ctxs), cu, 129, H, 1, D, bs, 0.09, sk, out)
+    assert torch.allclose(out[:, :H * D].float().cpu(), want, rtol=2e-2, atol=2e-2)
+    if sink:      # and the sink does take its share
+        plain = ops.attn_paged_wide(ctx, q, pool, pool, bt.to(DEV), i32(ctxs), cu, 129, bs, H, 1, D, D, 0.09).float().cpu()
+        assert (plain - want).abs().max() > 0.05
+
+
 # ------------------------------------------------------------------------------------------ output stages and activations
 @pytest.mark.parametrize("dt", DTS)
 def test_head_norm_with_a_shared_weight_and_a_silu_gate(ctx, ops, dt):
@@ -260,14 +288,16 @@ def plain_delta(x, offs, H, G, d, vd, conv_w, A_log, dt_bias, state):
 
 
 @pytest.mark.parametrize("form", ["token by token", "chunks"])
+@pytest.mark.parametrize("packed", [False, True])
 @pytest.mark.parametrize("H,G,d,vd,taps", [(4, 2, 16, 24, 4), (3, 3, 10, 36, 2), (2, 1, 64, 64, 3), (2, 2, 200, 8, 1), (1, 1, 128, 40, 5)])
-def test_delta_rule_carries_both_states_between_portions_and_slots(ctx, ops, H, G, d, vd, taps, form):
+def test_delta_rule_carries_both_states_between_portions_and_slots(ctx, ops, H, G, d, vd, taps, form, packed):
+    """packed: q, k, v stand beside one another from column 0 (rows that allow 16-byte accesses when the sizes do); else at odd columns."""
     max_qlen = 1 if form == "token by token" else 64
     g = torch.Generator().manual_seed(14)
     slots, qk = 4, G * d
     C = 2 * qk + H * vd
-    offs = (2, 2 + qk + 1, 2 + 2 * qk + 3, 2 + C + 4, 2 + C + 4 + H + 1)
-    ld = offs[4] + H + 2
+    offs = (0, qk, 2 * qk, C, C + H) if packed else (2, 2 + qk + 1, 2 + 2 * qk + 3, 2 + C + 4, 2 + C + 4 + H + 1)
+    ld = (offs[4] + H + 3) // 4 * 4 if packed else offs[4] + H + 2
     conv_w = torch.randn(C, taps, generator=g) * taps ** -0.5
     A_log, dt_bias = torch.log(0.3 + 2 * torch.rand(H, generator=g)), torch.randn(H, generator=g) * 0.5
     state = torch.randn(slots, H, d, vd, generator=g)                   # whatever an earlier owner left behind

@@ -44,15 +44,15 @@ def cfg_b(all_experts=False):
 
 
 def cfg_c(all_experts=False):
-    """Sizes of the tensor-pipe routes of the bf16 mode: cache rows of 64, 96 and 128 numbers (the 128-number row of a layer without
-    sink takes the tcgen05 kernel for long portions), latents that are multiples of 16, experts of 128 hidden units (grouped tcgen05
+    """Sizes of the tensor-pipe routes of the bf16 mode: cache rows of 64 and 128 numbers (128-number rows take the tcgen05 kernel
+    for long portions, with and without a sink), latents that are multiples of 16, experts of 128 hidden units (grouped tcgen05
     products), a delta head of 64 x 64."""
     return F.make_config(vocab=160, width=128, layers=[
         F.with_dense(F.latent_cfg(4, 32, 32, 32, 96, 64, scale=0.12, second=True), 192),
         F.with_moe(F.latent_cfg(6, 16, 16, 16, 48, 64, scale=0.2), 4, 2, 6 if all_experts else 2, 128, limit=1.5),
         F.with_dense(F.latent_cfg(2, 64, 32, 64, 96, 32, scale=0.1, second=True, kv_from=0), None),
         F.with_moe(F.delta_cfg(2, 1, 64, 64, conv=3), 3, 1, 4 if all_experts else 2, 160),
-        F.with_dense(F.latent_cfg(3, 16, 16, 48, 80, 48, scale=0.2), 64),
+        F.with_dense(F.latent_cfg(3, 16, 16, 48, 112, 48, scale=0.2), 64),
     ])
 
 
