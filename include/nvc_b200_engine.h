@@ -73,7 +73,9 @@ int nvc_runner_finalize(nvc_runner* r);
  * built-in body above), "Karuzen" (parallel layers with a Dynamic-Tanh norm, latent attention, dense or
  * mixture-of-experts feed-forward, a looped block of layers; fp32 residual stream) or "Ranilix" (parallel layers with two
  * RMS norms; windowed attention with a sink, value blending and an output gate, or causal attention beside retention with a
- * per-sequence recurrent state; squared-relu feed-forward; fp32 residual stream).  Error text:
+ * per-sequence recurrent state; squared-relu feed-forward; fp32 residual stream) or "Fefozen" (norms in front of and behind every
+ * sublayer; latent attention with a rotated key part, a sink and rows that a later layer may share; the gated delta rule with
+ * per-sequence recurrent and convolution state; dense or softmax-routed feed-forward with identity experts).  Error text:
  * nvc_model_config_last_error (thread-local). */
 typedef struct nvc_model_config nvc_model_config;
 const char* nvc_model_config_last_error(void);
@@ -97,7 +99,7 @@ int nvc_runner_takes_raw_tensors(const nvc_runner* r);
 /* 1 when every step of the runner attends through the paged cache (the engine then never calls nvc_runner_prefill). */
 int nvc_runner_needs_block_tables(const nvc_runner* r);
 int nvc_runner_vocab(const nvc_runner* r);
-/* Models with per-sequence recurrent state (Ranilix's retention) keep it in max_num_seqs state slots beside the paged cache:
+/* Models with per-sequence recurrent state (Ranilix's retention, Fefozen's delta rule) keep it in max_num_seqs state slots beside the paged cache:
  * nvc_runner_num_state_slots > 0, and before EVERY step the caller names the slot of each sequence of that step, in batch
  * order (distinct, in [0, slots)).  A sequence whose first token of a step sits at position 0 starts from an empty state;
  * any other continues from what its slot holds, so a slot belongs to one sequence from its first token to its last and a
