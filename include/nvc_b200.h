@@ -269,8 +269,8 @@ int nvc_prefill_attn_paged_ld(nvc_ctx* ctx, const nvc_bf16* q, int ldq, const nv
                               int total_q_tokens, int max_seqlen_q, int nh, int kv, int hd, int block_size,
                               int num_blocks, float scale, nvc_bf16* out, int ldo, void* stream);
 
-/* The same with a sink: sink (fp32 [nh], optional) adds one more term exp(sink_h) to the softmax denominator of every row of head
- * h; it has no key, is not scaled and carries no value. */
+/* The same with a sink: sink (fp32 [nh], optional) adds the term exp(sink_h), as it stands, to the softmax denominator of every row
+ * of head h; nothing is added to the numerator. */
 int nvc_prefill_attn_paged_sink(nvc_ctx* ctx, const nvc_bf16* q, int ldq, const nvc_bf16* k_cache,
                                 const nvc_bf16* v_cache, const int32_t* block_tables, int bt_stride,
                                 const int32_t* context_lens, const int32_t* cu_seqlens_q, int B,
