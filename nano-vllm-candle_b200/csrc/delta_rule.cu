@@ -502,7 +502,9 @@ extern "C" int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float*
     ctx->launches++;
     return NVC_OK;
   }
-  const int dpt = dim <= 16 ? 16 : (dim <= 32 ? 32 : (dim <= 64 ? 64 : 128));
+  // about four row groups per value column: four times the warps - and loads in flight - of one thread per whole column, at the price
+  // of one shared-memory reduction of three numbers per token
+  const int dpt = dim <= 64 ? 16 : (dim <= 128 ? 32 : (dim <= 256 ? 64 : 128));
   const int groups = (dim + dpt - 1) / dpt;
   const dim3 grid(p->B, p->heads, (p->vdim + 31) / 32), block(32 * groups);
   const size_t smem = ((size_t)4 * dim + (size_t)3 * groups * 32) * sizeof(float);
