@@ -505,7 +505,7 @@ int nvc_moe_combine_identity(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, 
                              const int32_t* topk_idx, int top, int E_real, const void* x, int x_dtype, int ldx, float* out, int ldo,
                              int N, int H, void* stream);
 /* Gated delta rule, the part between the fused projection and the recurrence, over the new tokens of every sequence:
- *   q, k, v channels: causal convolution over time per channel (conv_w [C, taps], last column = the current token; the taps - 1
+ *   q, k, v channels: causal convolution over time per channel (conv_w [taps, C], tap-major, last row = the current token; the taps - 1
  *   inputs in front of a portion come from conv_state [slots, taps - 1, C], zeros when the portion starts at position 0), silu;
  *   q and k heads: x / sqrt(sum(x^2) + unit_eps), q times q_scale;   beta = sigmoid(in[b_off + h]);
  *   decay = exp(-exp(A_log[h]) * softplus(in[a_off + h] + dt_bias[h])).
@@ -524,7 +524,7 @@ typedef struct nvc_delta_prep {
   float* gb_out;
   int B;
 } nvc_delta_prep;
-int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, void* stream);
+int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, int max_qlen, void* stream);   /* max_qlen: the longest portion (a bound will do) */
 /* The recurrence, per (sequence, head) with state S [dim, vdim] fp32 in state [slots, heads, dim, vdim]:
  *   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q        (head h reads q / k head h / (heads / kv_heads))
  * token by token over rows cu_seqlens[b] .. cu_seqlens[b + 1] (row b when cu_seqlens == NULL); a sequence starts from zeros when

@@ -124,7 +124,7 @@ def _declare(l: C.CDLL) -> None:
         "nvc_moe_route_logits_ex": [_vp, _vp, _i, _vp, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
         "nvc_moe_sort_padded_ex": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp],
         "nvc_moe_combine_identity": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _vp],
-        "nvc_delta_prep_run": [_vp, _vp, _i, _vp],
+        "nvc_delta_prep_run": [_vp, _vp, _i, _i, _vp],
         "nvc_delta_rule_scan": [_vp, _vp, _vp, _i, _vp, _i, _vp],
         "nvc_debug_set": [_i, _i],
     }

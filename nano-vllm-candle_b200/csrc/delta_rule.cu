@@ -2,7 +2,7 @@
 // and read in every token,
 //   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q,
 // with q, k, v taken through a short causal convolution over time per channel.  Three kernels:
-//   delta_prep_kernel   one warp per (token, unit): convolution + silu of a q / k / v head (the taps - 1 inputs in front of a
+//   delta_prep_kernel   one warp per (token, unit), the sequence from the block index: convolution + silu of a q / k / v head (the taps - 1 inputs in front of a
 //                       portion come from the sequence's convolution state), unit length for q and k, q scale; one more unit per token
 //                       for the per-head decay g = exp(-exp(A_log) softplus(a + dt_bias)) and beta = sigmoid(b)
 //   delta_scan_kernel   one CTA per (sequence, head, slice of 32 value columns); thread (column v, row group r) keeps rows
@@ -38,15 +38,19 @@ __device__ __forceinline__ int delta_find_seq(const int32_t* cu, int B, int row)
 
 __device__ __forceinline__ float softplus_f32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
+// grid (token tiles of the longest portion, units, sequences): the sequence comes from the block index, so a warp's first loads are
+// its sequence's bounds and nothing has to be searched; CTAs behind a sequence's last token leave at once
 __global__ void delta_prep_kernel(const DeltaArgs a) {
   pdl_trigger();
   pdl_wait();
   const nvc_delta_prep& p = a.p;
-  const int warps = blockDim.x >> 5, wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int units = 2 * p.kv_heads + p.heads + 1;
-  const int64_t u = (int64_t)blockIdx.x * warps + wid;
-  if (u >= (int64_t)a.N * units) return;
-  const int n = (int)(u / units), uu = (int)(u % units);
+  const int b = blockIdx.z, uu = blockIdx.y;
+  const int r0 = p.cu_seqlens ? p.cu_seqlens[b] : b;
+  const int r1 = p.cu_seqlens ? p.cu_seqlens[b + 1] : b + 1;
+  const int n = r0 + blockIdx.x * (blockDim.x >> 5) + wid;
+  if (n >= r1) return;
   const float* in = p.in + (int64_t)n * p.ldi;
   if (uu == units - 1) {
     // ---- decay and beta of every head
@@ -56,11 +60,6 @@ __global__ void delta_prep_kernel(const DeltaArgs a) {
       p.gb_out[(int64_t)n * 2 * p.heads + 2 * h + 1] = sigmoid_f32(in[p.b_off + h]);
     }
     return;
-  }
-  int b = n, r0 = n;
-  if (p.cu_seqlens) {
-    b = delta_find_seq(p.cu_seqlens, p.B, n);
-    r0 = p.cu_seqlens[b];
   }
   const int t = n - r0;                                 // index inside the portion
   const bool fresh = p.positions[r0] == 0;
@@ -85,17 +84,17 @@ __global__ void delta_prep_kernel(const DeltaArgs a) {
       const int j = 4 * lane + 128 * k;
       y[k] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (j < width) {
-        const float* w = p.conv_w + (int64_t)(ch + j) * p.taps;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int i = 0; i < p.taps; ++i) {
           const int src = t - (p.taps - 1) + i;
           float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
           if (src >= 0) x = *reinterpret_cast<const float4*>(in + (int64_t)(src - t) * p.ldi + col + j);
           else if (!fresh) x = *reinterpret_cast<const float4*>(cs + (int64_t)(p.taps - 1 + src) * C + ch + j);
-          acc.x = fmaf(__ldg(w + i), x.x, acc.x);
-          acc.y = fmaf(__ldg(w + p.taps + i), x.y, acc.y);
-          acc.z = fmaf(__ldg(w + 2 * p.taps + i), x.z, acc.z);
-          acc.w = fmaf(__ldg(w + 3 * p.taps + i), x.w, acc.w);
+          const float4 w = __ldg(reinterpret_cast<const float4*>(p.conv_w + (int64_t)i * C + ch + j));      // tap-major: lanes read side by side
+          acc.x = fmaf(w.x, x.x, acc.x);
+          acc.y = fmaf(w.y, x.y, acc.y);
+          acc.z = fmaf(w.z, x.z, acc.z);
+          acc.w = fmaf(w.w, x.w, acc.w);
         }
         y[k] = make_float4(acc.x * sigmoid_f32(acc.x), acc.y * sigmoid_f32(acc.y), acc.z * sigmoid_f32(acc.z), acc.w * sigmoid_f32(acc.w));
         ss4 += y[k].x * y[k].x + y[k].y * y[k].y + y[k].z * y[k].z + y[k].w * y[k].w;
@@ -112,14 +111,13 @@ __global__ void delta_prep_kernel(const DeltaArgs a) {
   }
   float ss = 0.f;
   for (int j = lane; j < width; j += 32) {
-    const float* w = p.conv_w + (int64_t)(ch + j) * p.taps;
     float acc = 0.f;
     for (int i = 0; i < p.taps; ++i) {
       const int src = t - (p.taps - 1) + i;             // portion index of the input under tap i
       float x;
       if (src >= 0) x = in[(int64_t)(src - t) * p.ldi + col + j];
       else x = fresh ? 0.f : cs[(int64_t)(p.taps - 1 + src) * C + ch + j];
-      acc = fmaf(__ldg(w + i), x, acc);
+      acc = fmaf(__ldg(p.conv_w + (int64_t)i * C + ch + j), x, acc);
     }
     const float y = acc * sigmoid_f32(acc);
     out[j] = y;
@@ -465,17 +463,21 @@ int check_prep(nvc_ctx* ctx, const nvc_delta_prep* p) {
 
 }  // namespace
 
-extern "C" int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, void* stream) {
+extern "C" int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, int max_qlen, void* stream) {
   int rc = check_prep(ctx, p);
   if (rc) return rc;
   NVC_REQUIRE(ctx, p->cu_seqlens || N == p->B, NVC_EINVAL, "rows without cu_seqlens: one per sequence");
   if (N == 0) return NVC_OK;
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   const int vec = p->dim % 4 == 0 && p->vdim % 4 == 0 && p->ldi % 4 == 0 && p->q_off % 4 == 0 && p->k_off % 4 == 0 && p->v_off % 4 == 0 && p->ldq % 4 == 0 &&
-                  p->ldk % 4 == 0 && p->ldv % 4 == 0 && al16(p->in) && al16(p->conv_state) && al16(p->q_out) && al16(p->k_out) && al16(p->v_out);
+                  p->ldk % 4 == 0 && p->ldv % 4 == 0 && al16(p->in) && al16(p->conv_state) && al16(p->conv_w) && al16(p->q_out) && al16(p->k_out) && al16(p->v_out);
   DeltaArgs a{*p, N, vec, nullptr, 0, nullptr};
-  const int64_t units = (int64_t)N * (2 * p->kv_heads + p->heads + 1);
-  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, delta_prep_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, nvc_stream(stream), a));
+  const int units = 2 * p->kv_heads + p->heads + 1;
+  const int longest = p->cu_seqlens ? std::min(N, std::max(max_qlen, 1)) : 1;
+  NVC_REQUIRE(ctx, units <= 65535 && p->B <= 65535, NVC_ESHAPE, "more than 65 535 heads or sequences");
+  const int warps = longest >= 4 ? 4 : 1;
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, delta_prep_kernel, dim3((unsigned)((longest + warps - 1) / warps), units, p->B), dim3(32 * warps), 0,
+                                 nvc_stream(stream), a));
   ctx->launches++;
   return NVC_OK;
 }

@@ -343,9 +343,16 @@ struct FefozenBody : nvc_body_base {
       else if (!latent && sub == "mix.v") rc = in_rows(w.v_off, ow);
       else if (!latent && sub == "mix.b") rc = in_rows(w.b_off, d.heads);
       else if (!latent && sub == "mix.a") rc = in_rows(w.a_off, d.heads);
-      else if (!latent && sub == "mix.q.conv") { if (!shape_is(qk, d.taps)) return bad(); rc = put_f32(r, w.conv_w, v.data(), n); }
-      else if (!latent && sub == "mix.k.conv") { if (!shape_is(qk, d.taps)) return bad(); rc = put_f32(r, w.conv_w + (size_t)qk * d.taps, v.data(), n); }
-      else if (!latent && sub == "mix.v.conv") { if (!shape_is(ow, d.taps)) return bad(); rc = put_f32(r, w.conv_w + (size_t)2 * qk * d.taps, v.data(), n); }
+      else if (!latent && (sub == "mix.q.conv" || sub == "mix.k.conv" || sub == "mix.v.conv")) {
+        // [channels, taps] of the checkpoint -> tap-major [taps, all channels] (q, k, v side by side): a warp's lanes read neighbours
+        const int rows = sub == "mix.v.conv" ? ow : qk, ch0 = sub == "mix.q.conv" ? 0 : (sub == "mix.k.conv" ? qk : 2 * qk), C = 2 * qk + ow;
+        if (!shape_is(rows, d.taps)) return bad();
+        std::vector<float> col(rows);
+        for (int i = 0; i < d.taps && rc == NVC_OK; ++i) {
+          for (int c = 0; c < rows; ++c) col[c] = v[(size_t)c * d.taps + i];
+          rc = put_f32(r, w.conv_w + (size_t)i * C + ch0, col.data(), rows);
+        }
+      }
       else if (!latent && sub == "mix.A_log") rc = vec(w.A_log, d.heads);
       else if (!latent && sub == "mix.dt_bias") rc = vec(w.dt_bias, d.heads);
       else if (!latent && sub == "mix.norm") rc = vec(w.onorm, d.vdim);
@@ -475,7 +482,7 @@ struct FefozenBody : nvc_body_base {
     p.q_out = rq; p.k_out = rk; p.v_out = rv; p.ldq = p.ldk = d.kv_heads * d.dim; p.ldv = d.heads * d.vdim;
     p.gb_out = gb;
     p.B = s.B;
-    int rc = nvc_delta_prep_run(ctx, &p, s.N, st);
+    int rc = nvc_delta_prep_run(ctx, &p, s.N, s.decode ? 1 : s.max_seqlen, st);
     if (rc) return rc;
     mark(r, "delta_prep");
     if ((rc = nvc_delta_rule_scan(ctx, &p, ro, p.ldv, w.state, s.decode ? 1 : s.max_seqlen, st))) return rc;

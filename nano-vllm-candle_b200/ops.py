@@ -681,7 +681,8 @@ def moe_combine_identity(ctx, y, pos, w, idx, E_real: int, x):
 
 def delta_rule(ctx, x, offs, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, conv_w, conv_state, state, state_slots, cu_seqlens,
                positions, A_log, dt_bias, unit_eps: float = 1e-6, q_scale: Optional[float] = None, max_qlen: int = 1 << 20):
-    """x: fp32 [N, ld] rows of the fused projection, offs = (q, k, v, beta, a) columns.  Runs the preparation and the recurrence;
+    """x: fp32 [N, ld] rows of the fused projection, offs = (q, k, v, beta, a) columns; conv_w: [taps, C] (tap-major).  Runs the
+    preparation and the recurrence;
     conv_state [slots, taps - 1, C] and state [slots, heads, dim, vdim] are updated in place.  Returns (o [N, heads * vdim], q, k, v, gb)."""
     N = x.shape[0]
     dev = x.device
@@ -693,6 +694,7 @@ def delta_rule(ctx, x, offs, heads: int, kv_heads: int, dim: int, vdim: int, tap
     p = DeltaPrepC(_a(x), x.stride(0), offs[0], offs[1], offs[2], offs[3], offs[4], heads, kv_heads, dim, vdim, taps, _a(conv_w), _a(conv_state),
                    _a(state_slots), _a(cu_seqlens), _a(positions), _a(A_log), _a(dt_bias), unit_eps, dim ** -0.5 if q_scale is None else q_scale,
                    _a(q), _a(k), _a(v), q.stride(0), k.stride(0), v.stride(0), _a(gb), state_slots.numel())
-    check(ctx.l.nvc_delta_prep_run(ctx.h, C.byref(p), N, _stream()), "nvc_delta_prep_run", ctx.h)
+    longest = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item()) if cu_seqlens is not None else 1
+    check(ctx.l.nvc_delta_prep_run(ctx.h, C.byref(p), N, longest, _stream()), "nvc_delta_prep_run", ctx.h)
     check(ctx.l.nvc_delta_rule_scan(ctx.h, C.byref(p), _ptr(o), o.stride(0), _ptr(state), max_qlen, _stream()), "nvc_delta_rule_scan", ctx.h)
     return o, q, k, v, gb

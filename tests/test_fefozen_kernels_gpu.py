@@ -311,7 +311,7 @@ def test_delta_rule_carries_both_states_between_portions_and_slots(ctx, ops, H, 
     slot_of = {"a": 2, "b": 0, "c": 3}
     # steps of (name, count): portions beside single tokens, in changing batch order, portions shorter than the taps
     sched = [[("a", 20), ("b", 1)], [("b", 1), ("a", 1), ("c", 33)], [("c", 2), ("b", 3), ("a", 16)], [("c", 62), ("b", 1)]]
-    kw = dict(heads=H, kv_heads=G, dim=d, vdim=vd, taps=taps, conv_w=conv_w.to(DEV), conv_state=cstate_d, state=state_d, A_log=A_log.to(DEV),
+    kw = dict(heads=H, kv_heads=G, dim=d, vdim=vd, taps=taps, conv_w=conv_w.t().contiguous().to(DEV), conv_state=cstate_d, state=state_d, A_log=A_log.to(DEV),
               dt_bias=dt_bias.to(DEV))
     for step in sched:
         cu, pos, xs = [0], [], []
@@ -357,7 +357,7 @@ def test_delta_rule_overwrites_what_a_key_held(ctx, ops):
     v5 = torch.nn.functional.silu(x[5, 2 * d:2 * d + vd])
     for max_qlen in (1, T):
         state, cstate = torch.zeros(1, H, d, vd, device=DEV), torch.zeros(1, 1, 2 * d + vd, device=DEV)
-        o, q, k, v, gb = ops.delta_rule(ctx, x.to(DEV), (0, d, 2 * d, 2 * d + vd, 2 * d + vd + 1), H, 1, d, vd, 1, conv_w.to(DEV), cstate, state, i32([0]),
+        o, q, k, v, gb = ops.delta_rule(ctx, x.to(DEV), (0, d, 2 * d, 2 * d + vd, 2 * d + vd + 1), H, 1, d, vd, 1, conv_w.t().contiguous().to(DEV), cstate, state, i32([0]),
                                         i32([0, T]), i32(list(range(T))), torch.zeros(1, device=DEV), torch.zeros(1, device=DEV), max_qlen=max_qlen)
         assert torch.allclose(o.cpu()[T - 1], v5 * d ** -0.5, rtol=1e-4, atol=1e-6)
 
@@ -375,7 +375,7 @@ def test_a_decay_that_underflows_inside_a_chunk(ctx, ops):
     outs = []
     for max_qlen in (1, T):
         state, cstate = torch.zeros(1, H, d, vd, device=DEV), torch.zeros(1, 1, 2 * d + H * vd, device=DEV)
-        o = ops.delta_rule(ctx, x.to(DEV), (0, d, 2 * d, 2 * d + H * vd, 2 * d + H * vd + H), H, 1, d, vd, 1, conv_w.to(DEV), cstate, state, i32([0]),
+        o = ops.delta_rule(ctx, x.to(DEV), (0, d, 2 * d, 2 * d + H * vd, 2 * d + H * vd + H), H, 1, d, vd, 1, conv_w.t().contiguous().to(DEV), cstate, state, i32([0]),
                            i32([0, T]), i32(list(range(T))), A_log.to(DEV), torch.zeros(H, device=DEV), max_qlen=max_qlen)[0].cpu()
         assert torch.isfinite(o).all()
         outs.append(o)
