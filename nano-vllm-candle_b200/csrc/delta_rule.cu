@@ -14,6 +14,8 @@
 //   delta_chunk_kernel  the same recurrence 32 tokens at a time for prompt portions (see there).
 // Both states live in fp32 in pools of state slots; a sequence whose first new token sits at position 0 starts from zeros.
 // Everything here is plain fp32 FMA code.
+#include <cooperative_groups.h>
+
 #include "typed.cuh"
 
 namespace {
@@ -26,15 +28,6 @@ struct DeltaArgs {
   int ldo;
   float* state;
 };
-
-__device__ __forceinline__ int delta_find_seq(const int32_t* cu, int B, int row) {
-  int lo = 0, hi = B - 1;      // largest b with cu[b] <= row
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (cu[mid] <= row) lo = mid; else hi = mid - 1;
-  }
-  return lo;
-}
 
 __device__ __forceinline__ float softplus_f32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
@@ -260,8 +253,12 @@ __device__ __forceinline__ float fma4(const float4& x, const float4& y, float ac
   return fmaf(x.w, y.w, acc);
 }
 
-template <int DPT>
+// kCluster: the CTAs of one (sequence, head) - its slices of 32 value columns - form a thread-block cluster, split the rows of the two
+// token-by-token matrices among themselves and write them into one another's shared memory: the products that do not depend on the
+// value column are computed once per (sequence, head), not once per slice.
+template <int DPT, bool kCluster>
 __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a) {
+  namespace cg = cooperative_groups;
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const nvc_delta_prep& p = a.p;
@@ -318,32 +315,48 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
     }
     __syncthreads();
     // ---- products between the chunk's tokens: two rows t per warp and pass, column j per lane, 16-byte operands
-    for (int t = 2 * w; t < kDC; t += 2 * kDW) {
-      float kk0 = 0.f, qk0 = 0.f, kk1 = 0.f, qk1 = 0.f;
-      if (lane <= t + 1) {
-        const float4* kt0 = reinterpret_cast<const float4*>(Ks + t * ds);
-        const float4* qt0 = reinterpret_cast<const float4*>(Qs + t * ds);
-        const float4* kt1 = reinterpret_cast<const float4*>(Ks + (t + 1) * ds);
-        const float4* qt1 = reinterpret_cast<const float4*>(Qs + (t + 1) * ds);
-        const float4* kj = reinterpret_cast<const float4*>(Ks + lane * ds);
+    {
+      const int Z = kCluster ? (int)gridDim.z : 1, zr = kCluster ? (int)blockIdx.z : 0;
+      for (int t = 2 * (zr + Z * w); t < kDC; t += 2 * Z * kDW) {
+        float kk0 = 0.f, qk0 = 0.f, kk1 = 0.f, qk1 = 0.f;
+        if (lane <= t + 1) {
+          const float4* kt0 = reinterpret_cast<const float4*>(Ks + t * ds);
+          const float4* qt0 = reinterpret_cast<const float4*>(Qs + t * ds);
+          const float4* kt1 = reinterpret_cast<const float4*>(Ks + (t + 1) * ds);
+          const float4* qt1 = reinterpret_cast<const float4*>(Qs + (t + 1) * ds);
+          const float4* kj = reinterpret_cast<const float4*>(Ks + lane * ds);
 #pragma unroll 2
-        for (int c = 0; c < dz / 4; ++c) {
-          const float4 x = kj[c];
-          kk0 = fma4(kt0[c], x, kk0);
-          qk0 = fma4(qt0[c], x, qk0);
-          kk1 = fma4(kt1[c], x, kk1);
-          qk1 = fma4(qt1[c], x, qk1);
+          for (int c = 0; c < dz / 4; ++c) {
+            const float4 x = kj[c];
+            kk0 = fma4(kt0[c], x, kk0);
+            qk0 = fma4(qt0[c], x, qk0);
+            kk1 = fma4(kt1[c], x, kk1);
+            qk1 = fma4(qt1[c], x, qk1);
+          }
+          const float e0 = expf(fminf(Ls[t] - Ls[lane], 0.f)), e1 = expf(fminf(Ls[t + 1] - Ls[lane], 0.f));
+          kk0 *= e0 * Bs[t];
+          qk0 *= e0;
+          kk1 *= e1 * Bs[t + 1];
+          qk1 *= e1;
         }
-        const float e0 = expf(fminf(Ls[t] - Ls[lane], 0.f)), e1 = expf(fminf(Ls[t + 1] - Ls[lane], 0.f));
-        kk0 *= e0 * Bs[t];
-        qk0 *= e0;
-        kk1 *= e1 * Bs[t + 1];
-        qk1 *= e1;
+        const float a0 = lane < t ? kk0 : 0.f, p0 = lane <= t ? qk0 : 0.f, a1 = lane < t + 1 ? kk1 : 0.f, p1 = lane <= t + 1 ? qk1 : 0.f;
+        if constexpr (kCluster) {
+          cg::cluster_group cl = cg::this_cluster();
+          for (int r = 0; r < Z; ++r) {
+            float* am = cl.map_shared_rank(Am, r);
+            float* pm = cl.map_shared_rank(Pm, r);
+            am[t * as + lane] = a0;
+            pm[t * as + lane] = p0;
+            am[(t + 1) * as + lane] = a1;
+            pm[(t + 1) * as + lane] = p1;
+          }
+        } else {
+          Am[t * as + lane] = a0;
+          Pm[t * as + lane] = p0;
+          Am[(t + 1) * as + lane] = a1;
+          Pm[(t + 1) * as + lane] = p1;
+        }
       }
-      Am[t * as + lane] = lane < t ? kk0 : 0.f;
-      Pm[t * as + lane] = lane <= t ? qk0 : 0.f;
-      Am[(t + 1) * as + lane] = lane < t + 1 ? kk1 : 0.f;
-      Pm[(t + 1) * as + lane] = lane <= t + 1 ? qk1 : 0.f;
     }
     // ---- what the state before the chunk says to every key and query: partial sums over this warp's rows, then over the warps
 #pragma unroll 1
@@ -378,6 +391,7 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
       }
       __syncthreads();
     }
+    if constexpr (kCluster) cg::this_cluster().sync();      // every slice's rows of the two matrices have arrived
     // ---- the triangular system, one value column per lane of warp 0
     if (w == 0) {
       float u[kDC];
@@ -433,7 +447,8 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
         S[i] = s0; S[i + 1] = s1; S[i + 2] = s2; S[i + 3] = s3;
       }
     }
-    __syncthreads();
+    if constexpr (kCluster) cg::this_cluster().sync();      // no slice writes the next chunk's rows into a neighbour that still reads these
+    else __syncthreads();
   }
   if (vok)
 #pragma unroll
@@ -445,11 +460,15 @@ template <int DPT>
 cudaError_t launch_delta_chunk(nvc_ctx* ctx, const DeltaArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_chunk_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(delta_chunk_kernel<DPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(delta_chunk_kernel<DPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  return nvc_launch(ctx, delta_chunk_kernel<DPT>, grid, dim3(kDW * 32), smem, st, a);
+  static const bool no_cluster = getenv("NVC_DELTA_CLUSTER") && atoi(getenv("NVC_DELTA_CLUSTER")) == 0;
+  if (grid.z >= 2 && grid.z <= 8 && !no_cluster)       // the value slices of a (sequence, head) as one cluster
+    return nvc_launch_cluster3(ctx, delta_chunk_kernel<DPT, true>, grid, dim3(kDW * 32), smem, st, dim3(1, 1, grid.z), a);
+  return nvc_launch(ctx, delta_chunk_kernel<DPT, false>, grid, dim3(kDW * 32), smem, st, a);
 }
 
 int check_prep(nvc_ctx* ctx, const nvc_delta_prep* p) {

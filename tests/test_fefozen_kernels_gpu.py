@@ -289,7 +289,8 @@ def plain_delta(x, offs, H, G, d, vd, conv_w, A_log, dt_bias, state):
 
 @pytest.mark.parametrize("form", ["token by token", "chunks"])
 @pytest.mark.parametrize("packed", [False, True])
-@pytest.mark.parametrize("H,G,d,vd,taps", [(4, 2, 16, 24, 4), (3, 3, 10, 36, 2), (2, 1, 64, 64, 3), (2, 2, 200, 8, 1), (1, 1, 128, 40, 5)])
+@pytest.mark.parametrize("H,G,d,vd,taps", [(4, 2, 16, 24, 4), (3, 3, 10, 36, 2), (2, 1, 64, 64, 3), (2, 2, 200, 8, 1), (1, 1, 128, 40, 5),
+                                           (2, 1, 32, 128, 4), (1, 1, 16, 300, 2)])      # 1, 2, 4 and 10 slices of 32 value columns
 def test_delta_rule_carries_both_states_between_portions_and_slots(ctx, ops, H, G, d, vd, taps, form, packed):
     """packed: q, k, v stand beside one another from column 0 (rows that allow 16-byte accesses when the sizes do); else at odd columns."""
     max_qlen = 1 if form == "token by token" else 64
