@@ -33,7 +33,7 @@ __device__ __forceinline__ float softplus_f32(float x) { return x > 20.f ? x : l
 
 // grid (token tiles of the longest portion, units, sequences): the sequence comes from the block index, so a warp's first loads are
 // its sequence's bounds and nothing has to be searched; CTAs behind a sequence's last token leave at once
-__global__ void delta_prep_kernel(const DeltaArgs a) {
+__global__ void __launch_bounds__(128, 8) delta_prep_kernel(const DeltaArgs a) {
   pdl_trigger();
   pdl_wait();
   const nvc_delta_prep& p = a.p;
