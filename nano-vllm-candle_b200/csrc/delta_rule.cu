@@ -253,6 +253,28 @@ __device__ __forceinline__ float fma4(const float4& x, const float4& y, float ac
   return fmaf(x.w, y.w, acc);
 }
 
+// Forward substitution of the chunk's triangular system, one value column per lane of one warp: Us holds v_t on entry and u_t on
+// return.  Fully unrolled (the u_t live in registers); not inlined, so that it is compiled once and not once per kernel variant.
+__device__ __noinline__ void delta_chunk_solve(const float* Am, float* Us, const float* W1, const float* Ls, const float* Bs, int lane) {
+  constexpr int as = kDAs;
+  float u[kDC];
+#pragma unroll
+  for (int t = 0; t < kDC; ++t) {
+    float x = Bs[t] * (Us[t * 32 + lane] - expf(Ls[t]) * W1[t * 32 + lane]);
+#pragma unroll
+    for (int j4 = 0; j4 < t; j4 += 4) {       // entries at and behind the diagonal are zero
+      const float4 am = *reinterpret_cast<const float4*>(Am + t * as + j4);
+      x = fmaf(-am.x, u[j4], x);
+      if (j4 + 1 < t) x = fmaf(-am.y, u[j4 + 1], x);
+      if (j4 + 2 < t) x = fmaf(-am.z, u[j4 + 2], x);
+      if (j4 + 3 < t) x = fmaf(-am.w, u[j4 + 3], x);
+    }
+    u[t] = x;
+  }
+#pragma unroll
+  for (int t = 0; t < kDC; ++t) Us[t * 32 + lane] = u[t];
+}
+
 // kCluster: the CTAs of one (sequence, head) - its slices of 32 value columns - form a thread-block cluster, split the rows of the two
 // token-by-token matrices among themselves and write them into one another's shared memory: the products that do not depend on the
 // value column are computed once per (sequence, head), not once per slice.
@@ -393,24 +415,7 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
     }
     if constexpr (kCluster) cg::this_cluster().sync();      // every slice's rows of the two matrices have arrived
     // ---- the triangular system, one value column per lane of warp 0
-    if (w == 0) {
-      float u[kDC];
-#pragma unroll
-      for (int t = 0; t < kDC; ++t) {
-        float x = Bs[t] * (Us[t * 32 + lane] - expf(Ls[t]) * W1[t * 32 + lane]);
-#pragma unroll
-        for (int j4 = 0; j4 < t; j4 += 4) {       // entries at and behind the diagonal are zero
-          const float4 am = *reinterpret_cast<const float4*>(Am + t * as + j4);
-          x = fmaf(-am.x, u[j4], x);
-          if (j4 + 1 < t) x = fmaf(-am.y, u[j4 + 1], x);
-          if (j4 + 2 < t) x = fmaf(-am.z, u[j4 + 2], x);
-          if (j4 + 3 < t) x = fmaf(-am.w, u[j4 + 3], x);
-        }
-        u[t] = x;
-      }
-#pragma unroll
-      for (int t = 0; t < kDC; ++t) Us[t * 32 + lane] = u[t];
-    }
+    if (w == 0) delta_chunk_solve(Am, Us, W1, Ls, Bs, lane);
     __syncthreads();
     // ---- outputs and the state behind the chunk
     {
@@ -432,19 +437,18 @@ __global__ void __launch_bounds__(kDW * 32) delta_chunk_kernel(const DeltaArgs a
       const float Ln = Ls[kDC - 1];
       const float gn = expf(Ln);
 #pragma unroll
-      for (int j = 0; j < kDC; ++j) uu[j] *= expf(Ln - Ls[j]);
+      for (int i = 0; i < DPT; ++i) S[i] *= gn;
+#pragma unroll 4
+      for (int j = 0; j < kDC; ++j) {             // a loop over the tokens around an unrolled pass over this thread's rows: short code
+        const float uj = Us[j * 32 + lane] * expf(Ln - Ls[j]);
 #pragma unroll
-      for (int i = 0; i < DPT; i += 4) {
-        float s0 = gn * S[i], s1 = gn * S[i + 1], s2 = gn * S[i + 2], s3 = gn * S[i + 3];
-#pragma unroll
-        for (int j = 0; j < kDC; ++j) {
+        for (int i = 0; i < DPT; i += 4) {
           const float4 x = *reinterpret_cast<const float4*>(Ks + j * ds + d0 + i);
-          s0 = fmaf(x.x, uu[j], s0);
-          s1 = fmaf(x.y, uu[j], s1);
-          s2 = fmaf(x.z, uu[j], s2);
-          s3 = fmaf(x.w, uu[j], s3);
+          S[i] = fmaf(x.x, uj, S[i]);
+          S[i + 1] = fmaf(x.y, uj, S[i + 1]);
+          S[i + 2] = fmaf(x.z, uj, S[i + 2]);
+          S[i + 3] = fmaf(x.w, uj, S[i + 3]);
         }
-        S[i] = s0; S[i + 1] = s1; S[i + 2] = s2; S[i + 3] = s3;
       }
     }
     if constexpr (kCluster) cg::this_cluster().sync();      // no slice writes the next chunk's rows into a neighbour that still reads these
@@ -507,18 +511,17 @@ extern "C" int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float*
   NVC_REQUIRE(ctx, o && state && ldo >= p->heads * p->vdim && max_qlen >= 1, NVC_EINVAL, "bad output / state");
   DeltaArgs a{*p, 0, 0, o, ldo, state};
   const int dim = p->dim;
-  if (p->cu_seqlens && max_qlen >= 8 && dim <= 512) {
-    // prompt portions: 32 tokens at a time
+  if (p->cu_seqlens && max_qlen >= 8 && dim <= 256) {
+    // prompt portions: 32 tokens at a time (keys of more than 256 numbers stay token by token)
     const int per = (dim + kDW - 1) / kDW;     // rows of the state per warp
-    const int cd = per <= 8 ? 8 : (per <= 16 ? 16 : (per <= 32 ? 32 : (per <= 64 ? 64 : 128)));
+    const int cd = per <= 8 ? 8 : (per <= 16 ? 16 : (per <= 32 ? 32 : 64));
     const dim3 grid(p->B, p->heads, (p->vdim + 31) / 32);
     const size_t smem = delta_chunk_smem_floats(dim, cd) * sizeof(float);
     cudaError_t ce;
     if (cd == 8) ce = launch_delta_chunk<8>(ctx, a, grid, smem, nvc_stream(stream));
     else if (cd == 16) ce = launch_delta_chunk<16>(ctx, a, grid, smem, nvc_stream(stream));
     else if (cd == 32) ce = launch_delta_chunk<32>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (cd == 64) ce = launch_delta_chunk<64>(ctx, a, grid, smem, nvc_stream(stream));
-    else ce = launch_delta_chunk<128>(ctx, a, grid, smem, nvc_stream(stream));
+    else ce = launch_delta_chunk<64>(ctx, a, grid, smem, nvc_stream(stream));
     NVC_CUDA_CHECK(ctx, ce);
     ctx->launches++;
     return NVC_OK;
