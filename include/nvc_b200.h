@@ -429,7 +429,11 @@ typedef struct nvc_qkv_prep {
   const int32_t* slot_mapping;
   int q_dtype, kv_dtype;
   float v_scale;                          /* v *= v_scale on the way out (after blending); a mixer's constant weight can ride here */
+  int unit_norm;                          /* q and k heads are divided by their root mean square (eps inside the root) without a weight;
+                                           * q_norm and k_norm must be NULL */
+  int act;                                /* NVC_PREP_ACT_SILU: q, k and v go through z sigmoid(z) right after the bias */
 } nvc_qkv_prep;
+enum { NVC_PREP_ACT_NONE = 0, NVC_PREP_ACT_SILU = 1 };
 int nvc_qkv_prep_run(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void* stream);
 /* Grouped-query softmax attention over a paged cache with separate key and value widths:
  *   out[i, h, :vdim] = out_scale * gate_i,h * sum_j p_j v_j,   p_j = exp(s_j) / (sum_j' exp(s_j') + exp(sink_h)),
@@ -445,6 +449,9 @@ typedef struct nvc_attn_spec {
   const float* sink;
   const float* gate; int ldg;
   float out_scale;
+  float softcap;             /* > 0: s_j <- softcap * tanh(s_j / softcap) */
+  int chunk;                 /* > 0 (window must be 0): j over pos_i - pos_i % chunk .. pos_i - the keys of the row's own chunk */
+  int gate_per_head;         /* the gate is fp32 [rows, ldg] with ONE number per head (column h) instead of one per output number */
 } nvc_attn_spec;
 int nvc_attn_paged_wide(nvc_ctx* ctx, const void* q, int ldq, const void* k_cache, int ldk, const void* v_cache, int ldv,
                         const int32_t* block_tables, int bt_stride, const int32_t* context_lens, const int32_t* cu_seqlens, int B,
@@ -531,6 +538,66 @@ int nvc_delta_prep_run(nvc_ctx* ctx, const nvc_delta_prep* p, int N, int max_qle
  * positions[first row] == 0; portions of 8 tokens and more (max_qlen) run 32 tokens at a time (the same sums regrouped, fp32 FMA).
  * Also advances the convolution state of nvc_delta_prep_run (p->in still holds the step's rows). */
 int nvc_delta_rule_scan(nvc_ctx* ctx, const nvc_delta_prep* p, float* o, int ldo, float* state, int max_qlen, void* stream);
+
+/* ---- mechanisms of the models with chunked capped attention beside a selective state space layer, lightning attention, a looped
+ * block with an input projection and input-weighted experts (Batatar) ---- */
+/* Residual accumulation with up to two branch outputs, each plain or RMS-normed with a weight first, and the norm in front of the
+ * next sublayer, in one pass over the row (all sums fp32):
+ *   f(y, w) = y (w == NULL) or y / sqrt(mean(y^2) + eps) * w;
+ *   s = res_in[r] + bias + c0 f(y0[r], w0) + c1 f(y1[r], w1)      (res_in, bias [H], y0, y1 optional);  res_out[r] = s (optional);
+ *   out[i, :H] = s / sqrt(mean(s^2) + eps) * w  (w != NULL)  or  s  (w == NULL, out != NULL: the sum in the storage format).
+ * rows as in nvc_rms_norm_pair (gathers; res_out must be NULL). */
+int nvc_rms_norm_blend(nvc_ctx* ctx, const float* res_in, const float* bias, const float* y0, const float* w0, float c0, const float* y1,
+                       const float* w1, float c1, float* res_out, int ld, const float* w, void* out, int out_dtype, int ldo, float eps,
+                       const int32_t* rows, int N, int H, void* stream);
+/* Output stage of a mixer whose norm spans groups of columns: per row, `groups` equal parts of gsize numbers;
+ *   gate_first != 0:  y = o * act(gate);  out = y / sqrt(mean_group(y^2) + eps) * weight
+ *   gate_first == 0:  out = o / sqrt(mean_group(o^2) + eps) * weight * act(gate)
+ * weight: fp32 [groups * gsize] (NULL: none); gate fp32 [N, ldg] (NULL: none); act: NVC_GATE_SIGMOID or NVC_GATE_SILU. */
+int nvc_group_norm_gate(nvc_ctx* ctx, const float* o, int ldo, const float* gate, int ldg, const float* weight, void* out, int ldout,
+                        int out_dtype, int groups, int gsize, int gate_first, float eps, int act, int N, void* stream);
+/* Linear recurrence with a decaying matrix state per (sequence, head), S [dim, vdim] fp32 in state [slots, heads, dim, vdim]:
+ *   S_t = d_t S_(t-1) + k_t v_t^T;   o_t = S_t^T q_t + skip_w[h] skip_t
+ * d_t = decay[h] (a constant per head) or exp(log_decay[t, h]) (per token and head, log_decay <= 0); head h reads q / k head
+ * h / (heads / qk_heads); skip optional.  Rows, slots, start from zeros and max_qlen as in nvc_retention_scan (which is this with
+ * decay, qk_heads = heads and no skip). */
+typedef struct nvc_decay_scan_args {
+  const float* q; const float* k; const float* v; int ldq, ldk, ldv;
+  float* o; int ldo;
+  float* state; const int32_t* state_slots; const int32_t* cu_seqlens; const int32_t* positions;
+  const float* decay;
+  const float* log_decay; int ldl;
+  const float* skip; const float* skip_w; int lds;
+  int heads, qk_heads, dim, vdim;
+} nvc_decay_scan_args;
+int nvc_decay_scan(nvc_ctx* ctx, const nvc_decay_scan_args* p, int B, int max_qlen, void* stream);
+/* Selective state space layer, the part between the fused projection and the recurrence, over the new tokens of every sequence.
+ * A projection row holds the convolution channels [x: heads * vdim | B: groups * state | C: groups * state] from column xbc_off and
+ * one step size per head from column dt_off.  Channels: causal convolution over time (conv_w [taps, C] tap-major, last row = the
+ * current token; bias conv_b; the taps - 1 inputs in front of a portion come from conv_state [slots, taps - 1, C], zeros when the
+ * portion starts at position 0), silu.  dt = softplus(in[dt_off + h] + dt_bias[h]).  Outputs (fp32 rows): x, v = dt x, B, C and
+ * log_decay[n, h] = -exp(A_log[h]) dt.  nvc_ssd_conv_advance then moves every sequence's convolution state past the step's rows. */
+typedef struct nvc_ssd_prep {
+  const float* in; int ldi;
+  int xbc_off, dt_off;
+  int heads, vdim, groups, state, taps;
+  const float* conv_w; const float* conv_b;
+  float* conv_state;
+  const int32_t* state_slots; const int32_t* cu_seqlens; const int32_t* positions;
+  const float* A_log; const float* dt_bias;
+  float* x_out; float* v_out; int ldx;
+  float* b_out; float* c_out; int ldbc;
+  float* log_decay; int ldl;
+  int B;
+} nvc_ssd_prep;
+int nvc_ssd_prep_run(nvc_ctx* ctx, const nvc_ssd_prep* p, int N, void* stream);
+int nvc_ssd_conv_advance(nvc_ctx* ctx, const nvc_ssd_prep* p, void* stream);
+/* Experts whose router weight multiplies their INPUT: out[pos[n * top + t], :H] = topk_w[n, t] * h[n, :H] in the storage format
+ * (the product in fp32, rounded once); pos from nvc_moe_sort or nvc_moe_sort_padded. */
+int nvc_moe_scatter_scaled(nvc_ctx* ctx, const void* h, int dtype, int ldh, const int32_t* pos, const float* topk_w, int top, void* out,
+                           int ldo, int N, int H, void* stream);
+/* NVC_ACT_SILU_MUL for nvc_act_mul_p: out[n, j] = silu(in[n, j]) * in[n, Fp + j]. */
+enum { NVC_ACT_SILU_MUL = 5 };
 
 /* K8. Replaces Qwen3ModelRunner::argmax (src/engine/llm_engine.rs:135-142) on device:
  * idx[b] = LAST index of the maximum of logits[b, :] (Iterator::max_by tie rule);

@@ -1,7 +1,8 @@
 // nvc_attn_paged_wide: grouped-query softmax attention over a paged cache whose keys and values have their own widths
-// (dim, vdim), with an optional sliding window, an optional sink term in the denominator, an optional sigmoid gate and a
-// constant factor on the output.  Rows of sequence b are the LAST q_len positions of its context; row at position i sees
-// keys max(0, i - window + 1) .. i (window == 0: 0 .. i).
+// (dim, vdim), with an optional sliding window or chunk mask, an optional cap on the scores (cap tanh(s / cap)), an optional sink
+// term in the denominator, an optional sigmoid gate (per output number or per head) and a constant factor on the output.  Rows of
+// sequence b are the LAST q_len positions of its context; row at position i sees keys max(0, i - window + 1) .. i (window), the
+// keys of its own chunk i - i % chunk .. i (chunk), or 0 .. i (neither).
 //
 // Two kernels:
 //   attn_wide_mma_kernel (attn_wide_mma.cuh)  bf16 storage, dim and vdim multiples of 16 up to 256: tensor pipe
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_wide_simt_kernel(const W
     qlen = a.cu_seqlens[b + 1] - r0;
   }
   const int pos = a.context_lens[b] - qlen + (row - r0);
-  const int lo = s.window > 0 ? max(0, pos - s.window + 1) : 0;
+  const int lo = widemma::first_visible(pos, s.window, s.chunk);
   const int g = h / (s.heads / s.kv_heads);
   const T* qp = reinterpret_cast<const T*>(a.q) + (int64_t)row * a.ldq + (int64_t)h * s.dim;
   for (int d = threadIdx.x; d < s.dim; d += blockDim.x) q_s[d] = ld_f(qp + d);
@@ -77,6 +78,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_wide_simt_kernel(const W
       float dot = 0.f;
       for (int d = 0; d < s.dim; ++d) dot = fmaf(q_s[d], ld_f(kp + d), dot);
       sc = dot * s.scale;
+      if (s.softcap > 0.f) sc = s.softcap * tanhf(sc / s.softcap);
     }
     const float mn = fmaxf(m, warp_max(sc));     // finite: the tile's first key is visible
     const float p = valid ? expf(sc - mn) : 0.f;
@@ -117,7 +119,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_wide_simt_kernel(const W
 #pragma unroll
     for (int w = 0; w < kSimtWarps; ++w) o += acc_s[w * s.vdim + c] * f[w];
     o *= inv;
-    if (s.gate) o *= sigmoid_f32(s.gate[(int64_t)row * s.ldg + (int64_t)h * s.vdim + c]);
+    if (s.gate) o *= sigmoid_f32(s.gate[(int64_t)row * s.ldg + (s.gate_per_head ? (int64_t)h : (int64_t)h * s.vdim + c)]);
     st_f(op + c, o * s.out_scale);
   }
 }
@@ -134,7 +136,9 @@ extern "C" int nvc_attn_paged_wide(nvc_ctx* ctx, const void* q, int ldq, const v
   NVC_REQUIRE(ctx, cu_seqlens || rows == B, NVC_EINVAL, "rows without cu_seqlens: one per sequence");
   NVC_REQUIRE(ctx, s.heads > 0 && s.kv_heads > 0 && s.heads % s.kv_heads == 0 && s.dim > 0 && s.vdim > 0 && s.dim <= 512 && s.vdim <= 512,
               NVC_ESHAPE, "heads / kv_heads / dim / vdim (dim, vdim <= 512)");
-  NVC_REQUIRE(ctx, s.window >= 0 && (!s.gate || s.ldg >= s.heads * s.vdim), NVC_EINVAL, "bad window / gate");
+  NVC_REQUIRE(ctx, s.window >= 0 && s.chunk >= 0 && !(s.window > 0 && s.chunk > 0) && s.softcap >= 0.f &&
+                       (!s.gate || s.ldg >= (s.gate_per_head ? s.heads : s.heads * s.vdim)),
+              NVC_EINVAL, "bad window / chunk / cap / gate");
   NVC_REQUIRE(ctx, ldq >= s.heads * s.dim && ldk >= s.kv_heads * s.dim && ldv >= s.kv_heads * s.vdim && ldo >= s.heads * s.vdim, NVC_EINVAL,
               "bad strides");
   WideArgs a{q, k_cache, v_cache, out, ldq, ldk, ldv, ldo, block_tables, context_lens, cu_seqlens, bt_stride, B, block_size, s};

@@ -1,5 +1,5 @@
 // Tensor-pipe kernel of nvc_attn_paged_wide (bf16 storage, included by attn_wide.cu only): grouped-query softmax attention with
-// separate key and value widths, a sliding window, a sink, a sigmoid gate and a constant factor.
+// separate key and value widths, a sliding window or a chunk mask, capped scores, a sink, a sigmoid gate and a constant factor.
 //
 // The M dimension of mma.sync.m16n8k16 holds 16 (token, head) rows of ONE sequence and ONE key / value head: the heads / kv_heads
 // query heads that share a key head are packed beside one another, so a key / value tile is loaded once for all of them.  Every
@@ -46,7 +46,17 @@ struct Args {
   const float* gate;
   int ldg;
   float out_scale;
+  int chunk;                 // > 0: a row sees the keys of its own chunk of that many positions only
+  float cap_log2e;           // > 0: scores are cap tanh(s / cap): cap * log2(e) here and scale / cap in scale_log2e
+  int gate_per_head;         // the gate holds one number per head instead of one per output number
 };
+
+// first key a row at position pos sees (both rules are monotone in pos)
+__host__ __device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  return window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : (chunk > 0 ? pos - pos % chunk : 0);
+}
+// tanh from one exp2 and one division: absolute error of a few 1e-7, exact limits at both ends
+__device__ __forceinline__ float tanh_exp2(float x) { return 1.0f - __fdividef(2.0f, fast_exp2(x * (2.0f * kLog2e)) + 1.0f); }
 
 template <int DKM, int DVM> constexpr int smem_bytes() {
   constexpr int ring = kStages * kCtaTok * (DKM + DVM) * 2;
@@ -59,7 +69,7 @@ template <int DKM, int DVM> constexpr int smem_bytes() {
 template <int DKM, int DVM, int NSUB>
 __device__ __forceinline__ void softmax_step(uint32_t stK, uint32_t stV, int tok0, int nsub, int ks_n, int nt_n, const uint32_t (*qa)[4],
                                              float (*o)[4], float& m0, float& m1, float& l0, float& l1, int lo_a, int hi_a, int lo_b, int hi_b,
-                                             float scale_log2e, bool all_visible, int lane) {
+                                             float scale_log2e, float cap_log2e, bool all_visible, int lane) {
   constexpr int RBK = DKM * 2, RBV = DVM * 2, KS = DKM / 16, NT = DVM / 8;
   const int tq = lane & 3;
   float s[2 * NSUB][4];
@@ -87,6 +97,14 @@ __device__ __forceinline__ void softmax_step(uint32_t stK, uint32_t stV, int tok
   }
   // columns tok0 + 8 jn + 2 tq + {0, 1}; a sub-tile that was not computed lies behind every row's bound
   float mx0 = -INFINITY, mx1 = -INFINITY;
+  if (cap_log2e > 0.f) {       // scale_log2e carries scale / cap: the capped score, already in the log2 domain, needs no further factor
+#pragma unroll
+    for (int jn = 0; jn < 2 * NSUB; ++jn) {
+      s[jn][0] = cap_log2e * tanh_exp2(s[jn][0] * scale_log2e); s[jn][1] = cap_log2e * tanh_exp2(s[jn][1] * scale_log2e);
+      s[jn][2] = cap_log2e * tanh_exp2(s[jn][2] * scale_log2e); s[jn][3] = cap_log2e * tanh_exp2(s[jn][3] * scale_log2e);
+    }
+    scale_log2e = 1.f;
+  }
   if (all_visible) {
 #pragma unroll
     for (int jn = 0; jn < 2 * NSUB; ++jn) {
@@ -194,7 +212,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
   const int ta = va ? ra / hg : 0, tb = vb ? rb / hg : 0;
   const int ha = g * hg + (va ? ra - ta * hg : 0), hb = g * hg + (vb ? rb - tb * hg : 0);
   const int hi_a = va ? base + ta : -1, hi_b = vb ? base + tb : -1;
-  const int lo_a = a.window > 0 ? max(0, hi_a - a.window + 1) : 0, lo_b = a.window > 0 ? max(0, hi_b - a.window + 1) : 0;
+  const int lo_a = first_visible(hi_a, a.window, a.chunk), lo_b = first_visible(hi_b, a.window, a.chunk);
   // Q as A fragments (rows past the end are zero)
   uint32_t qa[KS][4];
   {
@@ -256,12 +274,12 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
   if (many) {
     const int last_c = min(r0c + 16 * kWarps - 1, total - 1);
     const int kmax_cta = base + last_c / hg;
-    const int kmin_cta = a.window > 0 ? max(0, base + r0c / hg - a.window + 1) : 0;
+    const int kmin_cta = first_visible(base + r0c / hg, a.window, a.chunk);
     const int kmax_w = r0 < total ? base + min(r0 + 15, total - 1) / hg : -1;    // a warp past the end only loads
     const int first_w = base + r0 / hg;                                          // position of the warp's first row
-    const int kmin_w = a.window > 0 ? max(0, first_w - a.window + 1) : 0;
+    const int kmin_w = first_visible(first_w, a.window, a.chunk);
     // a tile is wholly visible to every row of the warp when it lies in [lo of the LAST row, hi of the FIRST row]
-    const int lo_last = a.window > 0 ? max(0, kmax_w - a.window + 1) : 0;
+    const int lo_last = first_visible(kmax_w, a.window, a.chunk);
     const int tile0 = kmin_cta / kCtaTok;
     const int n_tiles = kmax_cta / kCtaTok + 1 - tile0;
     const uint32_t ring = smem_u32(smem);
@@ -284,17 +302,17 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
       const int nsub = min(kCtaTok / 16, (kmax_w - tok0) / 16 + 1);
       const bool all_visible = tok0 >= lo_last && tok0 + kCtaTok - 1 <= first_w;     // (rows past the end have q = 0: finite, never stored)
       softmax_step<DKM, DVM, kCtaTok / 16>(st, st + kTileK, tok0, nsub, ks_n, nt_n, qa, o, m0, m1, l0, l1, lo_a, hi_a, lo_b, hi_b, a.scale_log2e,
-                                           all_visible, lane);
+                                           a.cap_log2e, all_visible, lane);
     }
     cp_async_wait<0>();
   } else {
     // few rows: the four warps split the KEYS of one 16-row chunk
     const int last_row = min(r0 + 15, total - 1);
     const int kmax = base + last_row / hg;
-    const int kmin = a.window > 0 ? max(0, base + r0 / hg - a.window + 1) : 0;
+    const int kmin = first_visible(base + r0 / hg, a.window, a.chunk);
     const int first = (kmin / kCtaTok) * kCtaTok + warp * 16;       // this warp's first 16-token tile
     const int hi_first = base + r0 / hg;                            // the chunk's first row sees the least far ahead,
-    const int lo_last = a.window > 0 ? max(0, kmax - a.window + 1) : 0;   // its last row the least far back
+    const int lo_last = first_visible(kmax, a.window, a.chunk);   // its last row the least far back
     const int n_tiles = kmax >= first ? (kmax - first) / kCtaTok + 1 : 0;
     constexpr int kWarpStage = 16 * (RBK + RBV);
     const uint32_t ring = smem_u32(smem) + warp * (kStages * kWarpStage);
@@ -311,7 +329,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
       const uint32_t st = ring + (i % kStages) * kWarpStage;
       const int tok0 = first + i * kCtaTok;
       softmax_step<DKM, DVM, 1>(st, st + 16 * RBK, tok0, 1, ks_n, nt_n, qa, o, m0, m1, l0, l1, lo_a, hi_a, lo_b, hi_b, a.scale_log2e,
-                                tok0 >= lo_last && tok0 + 15 <= hi_first, lane);
+                                a.cap_log2e, tok0 >= lo_last && tok0 + 15 <= hi_first, lane);
       __syncwarp();
     }
     cp_async_wait<0>();
@@ -332,19 +350,24 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
     const float i0 = l0 > 0.f ? f0 * a.out_scale / l0 : 0.f, i1 = l1 > 0.f ? f1 * a.out_scale / l1 : 0.f;
     nvc_bf16* o0 = a.out + (int64_t)(row_begin + ta) * a.ldo + (int64_t)ha * a.dv;
     nvc_bf16* o1 = a.out + (int64_t)(row_begin + tb) * a.ldo + (int64_t)hb * a.dv;
-    const float* g0 = a.gate ? a.gate + (int64_t)(row_begin + ta) * a.ldg + (int64_t)ha * a.dv : nullptr;
-    const float* g1 = a.gate ? a.gate + (int64_t)(row_begin + tb) * a.ldg + (int64_t)hb * a.dv : nullptr;
+    const float* g0 = a.gate && !a.gate_per_head ? a.gate + (int64_t)(row_begin + ta) * a.ldg + (int64_t)ha * a.dv : nullptr;
+    const float* g1 = a.gate && !a.gate_per_head ? a.gate + (int64_t)(row_begin + tb) * a.ldg + (int64_t)hb * a.dv : nullptr;
+    float i0h = 1.f, i1h = 1.f;
+    if (a.gate && a.gate_per_head) {
+      if (va) i0h = sigmoid_f32(a.gate[(int64_t)(row_begin + ta) * a.ldg + ha]);
+      if (vb) i1h = sigmoid_f32(a.gate[(int64_t)(row_begin + tb) * a.ldg + hb]);
+    }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       if (nt < nt_n) {
         const int d = nt * 8 + 2 * tq;
         if (va) {
-          float x = o[nt][0] * i0, y = o[nt][1] * i0;
+          float x = o[nt][0] * i0 * i0h, y = o[nt][1] * i0 * i0h;
           if (g0) { x *= sigmoid_f32(g0[d]); y *= sigmoid_f32(g0[d + 1]); }
           *reinterpret_cast<uint32_t*>(o0 + d) = pack_bf16(x, y);
         }
         if (vb) {
-          float x = o[nt][2] * i1, y = o[nt][3] * i1;
+          float x = o[nt][2] * i1 * i1h, y = o[nt][3] * i1 * i1h;
           if (g1) { x *= sigmoid_f32(g1[d]); y *= sigmoid_f32(g1[d + 1]); }
           *reinterpret_cast<uint32_t*>(o1 + d) = pack_bf16(x, y);
         }
@@ -389,7 +412,7 @@ __global__ void __launch_bounds__(kWarps * 32) attn_wide_mma_kernel(const Args a
       O += sm_o[(w * 16 + rr) * DVM + d] * wt;
     }
     float y = L > 0.f ? O / L * a.out_scale : 0.f;
-    if (a.gate) y *= sigmoid_f32(a.gate[(int64_t)(row_begin + t) * a.ldg + (int64_t)h * a.dv + d]);
+    if (a.gate) y *= sigmoid_f32(a.gate[(int64_t)(row_begin + t) * a.ldg + (a.gate_per_head ? (int64_t)h : (int64_t)h * a.dv + d)]);
     a.out[(int64_t)(row_begin + t) * a.ldo + (int64_t)h * a.dv + d] = __bfloat16_as_ushort(__float2bfloat16_rn(y));
   }
 }
@@ -401,7 +424,7 @@ namespace {
 inline bool attn_wide_mma_takes(const nvc_attn_spec& s, int ldq, int ldk, int ldv, int ldo, int block_size) {
   static const bool off = getenv("NVC_ATTN_WIDE_MMA") && atoi(getenv("NVC_ATTN_WIDE_MMA")) == 0;
   return !off && s.dim % 16 == 0 && s.vdim % 16 == 0 && s.dim <= 128 && s.vdim <= 128 && ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 &&
-         ldo % 2 == 0 && block_size > 0 && (!s.gate || s.ldg % 2 == 0);
+         ldo % 2 == 0 && block_size > 0 && (!s.gate || s.gate_per_head || s.ldg % 2 == 0);
 }
 
 template <int DKM, int DVM>
@@ -426,7 +449,8 @@ inline int attn_wide_mma_launch(nvc_ctx* ctx, const void* q, const void* k_cache
   if (s.kv_heads > 65535 || B > 65535) return NVC_ENOTIMPL;
   widemma::Args a{reinterpret_cast<const nvc_bf16*>(q), reinterpret_cast<const nvc_bf16*>(k_cache), reinterpret_cast<const nvc_bf16*>(v_cache),
                   reinterpret_cast<nvc_bf16*>(out), ldq, ldk, ldv, ldo, block_tables, context_lens, cu_seqlens, bt_stride, block_size,
-                  s.heads, s.kv_heads, s.dim, s.vdim, s.scale * widemma::kLog2e, s.window, s.sink, s.gate, s.ldg, s.out_scale};
+                  s.heads, s.kv_heads, s.dim, s.vdim, s.softcap > 0.f ? s.scale / s.softcap : s.scale * widemma::kLog2e, s.window, s.sink, s.gate, s.ldg,
+                  s.out_scale, s.chunk, s.softcap * widemma::kLog2e, s.gate_per_head};
   const dim3 grid(gx, B, s.kv_heads);
   const bool k64 = s.dim <= 64, v64 = s.vdim <= 64;
   if (k64 && v64) return attn_wide_mma_launch_t<64, 64>(ctx, a, grid, stream);

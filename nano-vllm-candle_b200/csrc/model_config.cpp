@@ -264,6 +264,91 @@ int parse_fefozen(const JValue& root, nvc_fefozen_config& c) {
   return NVC_OK;
 }
 
+int parse_batatar(const JValue& root, nvc_batatar_config& c) {
+  std::string err;
+  if (!get_int(&root, "vocab", c.vocab, 1, err) || !get_int(&root, "width", c.width, 1, err) ||
+      !get_float(&root, "residual_mult", c.residual_mult, err))
+    return cfg_fail(err);
+  const JValue* norm = root.get("norm");
+  if (!norm || norm->kind != JValue::Obj || !get_float(norm, "eps", c.eps, err)) return cfg_fail("norm.eps: " + err);
+  const JValue* layers = root.get("layers");
+  if (!layers || layers->kind != JValue::Arr || layers->arr.empty()) return cfg_fail("`layers` must be a non-empty list");
+  for (size_t i = 0; i < layers->arr.size(); ++i) {
+    const JValue& jl = layers->arr[i];
+    const std::string where = "layers[" + std::to_string(i) + "]: ";
+    if (jl.kind != JValue::Obj) return cfg_fail(where + "not an object");
+    nvc_batatar_layer L;
+    const JValue* type = jl.get("type");
+    const JValue* m = jl.get("mixer");
+    if (!type || type->kind != JValue::Str) return cfg_fail(where + "missing `type`");
+    if (!m || m->kind != JValue::Obj) return cfg_fail(where + "missing `mixer`");
+    if (type->str == "parallel") {
+      L.kind = nvc_batatar_layer::Parallel;
+      const JValue* l = m->get("left");
+      const JValue* r = m->get("right");
+      if (!l || l->kind != JValue::Obj || !r || r->kind != JValue::Obj) return cfg_fail(where + "a parallel mixer needs `left` and `right`");
+      auto& a = L.attn;
+      if (!get_int(l, "heads", a.heads, 1, err) || !get_int(l, "kv_heads", a.kv_heads, 1, err) || !get_int(l, "dim", a.dim, 1, err) ||
+          !get_int(l, "vdim", a.vdim, 1, err) || !get_float(l, "scale", a.scale, err))
+        return cfg_fail(where + "mixer.left: " + err);
+      if (a.heads % a.kv_heads != 0) return cfg_fail(where + "mixer.left: heads must be a multiple of kv_heads");
+      if (const JValue* cap = l->get("softcap"); cap && cap->kind != JValue::Null) {
+        if (!get_float(l, "softcap", a.softcap, err) || !(a.softcap > 0.f)) return cfg_fail(where + "mixer.left: softcap must be a positive number");
+      }
+      if (const JValue* mask = l->get("mask"); mask && mask->kind != JValue::Null) {
+        if (mask->kind != JValue::Obj || !get_int(mask, "size", a.chunk, 1, err)) return cfg_fail(where + "mixer.left.mask: " + err);
+      }
+      auto& d = L.ssd;
+      if (!get_int(r, "heads", d.heads, 1, err) || !get_int(r, "vdim", d.vdim, 1, err) || !get_int(r, "state", d.state, 1, err) ||
+          !get_int(r, "groups", d.groups, 1, err) || !get_int(r, "conv", d.taps, 1, err) || !get_int(r, "norm_groups", d.norm_groups, 1, err))
+        return cfg_fail(where + "mixer.right: " + err);
+      if (d.heads % d.groups != 0) return cfg_fail(where + "mixer.right: heads must be a multiple of groups");
+      if ((d.heads * d.vdim) % d.norm_groups != 0) return cfg_fail(where + "mixer.right: heads * vdim must be a multiple of norm_groups");
+      if (d.taps > 16) return cfg_fail(where + "mixer.right: at most 16 taps");
+    } else if (type->str == "lightning") {
+      L.kind = nvc_batatar_layer::Lightning;
+      auto& a = L.lin;
+      if (!get_int(m, "heads", a.heads, 1, err) || !get_int(m, "dim", a.dim, 1, err) || !get_int(m, "vdim", a.vdim, 1, err))
+        return cfg_fail(where + "mixer: " + err);
+      const JValue* dec = m->get("decay");
+      if (!dec || dec->kind != JValue::Arr || (int)dec->arr.size() != a.heads) return cfg_fail(where + "mixer.decay must list one number per head");
+      for (const JValue& v : dec->arr) {
+        if (v.kind != JValue::Num || v.num < 0.0 || v.num > 1.0) return cfg_fail(where + "mixer.decay: numbers in [0, 1]");
+        a.decay.push_back((float)v.num);
+      }
+    } else {
+      return cfg_fail(where + "mixer type `" + type->str + "` is not supported");
+    }
+    const JValue* mlp = jl.get("mlp");
+    if (mlp && mlp->kind == JValue::Obj) {
+      const JValue* kind = mlp->get("kind");
+      if (!kind || kind->kind != JValue::Str) return cfg_fail(where + "mlp: missing `kind`");
+      if (kind->str != "moe") return cfg_fail(where + "mlp kind `" + kind->str + "` is not supported");
+      L.mlp.kind = nvc_routed_mlp_spec::Moe;
+      const JValue* r = mlp->get("router");
+      const JValue* e = mlp->get("expert");
+      if (!r || !e) return cfg_fail(where + "mlp: a mixture of experts needs `router` and `expert`");
+      if (!get_int(r, "experts", L.mlp.experts, 1, err) || !get_int(r, "top", L.mlp.top, 1, err) || !get_int(e, "ff", L.mlp.expert_ff, 1, err))
+        return cfg_fail(where + "mlp: " + err);
+      if (L.mlp.top > L.mlp.experts) return cfg_fail(where + "mlp: top exceeds the experts");
+      if (L.mlp.experts > 256) return cfg_fail(where + "mlp: at most 256 experts");
+    } else if (mlp && mlp->kind != JValue::Null) {
+      return cfg_fail(where + "`mlp` must be an object or null");
+    }
+    c.layers.push_back(L);
+  }
+  const JValue* loop = root.get("loop");
+  if (loop && loop->kind == JValue::Obj) {
+    c.looped = true;
+    if (!get_int(loop, "start", c.loop_start, 0, err) || !get_int(loop, "stop", c.loop_stop, 0, err) || !get_int(loop, "times", c.loop_times, 1, err))
+      return cfg_fail("loop: " + err);
+    if (c.loop_start >= c.loop_stop || c.loop_stop > (int)c.layers.size()) return cfg_fail("loop: 0 <= start < stop <= number of layers");
+  } else if (loop && loop->kind != JValue::Null) {
+    return cfg_fail("`loop` must be an object or null");
+  }
+  return NVC_OK;
+}
+
 }  // namespace
 
 std::vector<nvc_karuzen_config::Run> nvc_karuzen_config::runs() const {
@@ -272,6 +357,20 @@ std::vector<nvc_karuzen_config::Run> nvc_karuzen_config::runs() const {
   for (int t = 0; t < (loop_stop > loop_start ? loop_times : 0); ++t)
     for (int i = loop_start; i < loop_stop; ++i) out.push_back({i, t, t > 0 && i == loop_start});
   for (int i = loop_stop; i < (int)layers.size(); ++i) out.push_back({i, 0, false});
+  return out;
+}
+
+std::vector<nvc_batatar_config::Run> nvc_batatar_config::runs() const {
+  std::vector<Run> out;
+  const int n = (int)layers.size();
+  if (!looped) {
+    for (int i = 0; i < n; ++i) out.push_back({i, 0, false});
+    return out;
+  }
+  for (int i = 0; i < loop_start; ++i) out.push_back({i, 0, false});
+  for (int t = 0; t < loop_times; ++t)
+    for (int i = loop_start; i < loop_stop; ++i) out.push_back({i, t, i == loop_start});
+  for (int i = loop_stop; i < n; ++i) out.push_back({i, 0, false});
   return out;
 }
 
@@ -301,10 +400,12 @@ int nvc_model_config_from_json(const char* text, nvc_model_config** out) {
     rc = parse_ranilix(root, c->ranilix);
   } else if (arch == "Fefozen") {
     rc = parse_fefozen(root, c->fefozen);
+  } else if (arch == "Batatar") {
+    rc = parse_batatar(root, c->batatar);
   } else if (arch == "Qwen3ForCausalLM") {
     // parsed by nvc_qwen3_config_from_hf_dir (hf_loader.cpp) when loaded from a directory
   } else {
-    rc = cfg_fail("architecture `" + arch + "` is not registered (known: Qwen3ForCausalLM, Karuzen, Ranilix, Fefozen)");
+    rc = cfg_fail("architecture `" + arch + "` is not registered (known: Qwen3ForCausalLM, Karuzen, Ranilix, Fefozen, Batatar)");
   }
   if (rc) { delete c; return rc; }
   *out = c;
@@ -330,6 +431,7 @@ int nvc_model_config_vocab(const nvc_model_config* c) {
   if (!c) return 0;
   if (c->architecture == "Ranilix") return c->ranilix.vocab;
   if (c->architecture == "Fefozen") return c->fefozen.vocab;
+  if (c->architecture == "Batatar") return c->batatar.vocab;
   return c->architecture == "Karuzen" ? c->karuzen.vocab : c->qwen3.vocab_size;
 }
 int nvc_model_config_layer_runs(const nvc_model_config* c, int32_t* layers, int32_t* passes, int32_t* readd, int capacity) {
@@ -341,6 +443,15 @@ int nvc_model_config_layer_runs(const nvc_model_config* c, int32_t* layers, int3
       if (readd) readd[i] = 0;
     }
     return n;
+  }
+  if (c && c->architecture == "Batatar") {      // readd = 1 where a pass of the looped block opens
+    const auto runs = c->batatar.runs();
+    for (int i = 0; i < (int)runs.size() && i < capacity; ++i) {
+      if (layers) layers[i] = runs[i].layer;
+      if (passes) passes[i] = runs[i].pass;
+      if (readd) readd[i] = runs[i].opens_pass ? 1 : 0;
+    }
+    return (int)runs.size();
   }
   if (!c || c->architecture != "Karuzen") return NVC_EINVAL;
   const auto runs = c->karuzen.runs();

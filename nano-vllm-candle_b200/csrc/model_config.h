@@ -118,11 +118,52 @@ struct nvc_fefozen_config {
   }
 };
 
+// Batatar: a stack of sequential pre-normed layers on an fp32 residual stream with one constant factor on both branches,
+// x <- x + m mixer(n1(x)), x <- x + m ff(n2(x)).  Mixers: "parallel" - grouped-query attention without positions (biases, unit-rms
+// q and k heads, capped scores, keys of the query's own chunk only, a sink of score zero, one sigmoid gate per head) beside a
+// selective state space layer (short convolution, a decay per token and head, a grouped gated norm), each side normed over the
+// width, halved and summed - or "lightning" (linear attention with a constant decay per head, one norm over all heads, a sigmoid
+// gate).  Feed-forward: sigmoid-routed experts whose router weight multiplies their input.  A block of layers may run several
+// passes with the same weights; every pass has its own cache and state and opens with a projection of [x ; embedding] and a
+// vector of its own.
+struct nvc_chunk_attn_spec {
+  int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
+  float scale = 0.f;
+  float softcap = 0.f;       // 0: scores are not capped
+  int chunk = 0;             // 0: every earlier token is visible; n: position i sees j <= i with floor(i / n) = floor(j / n)
+};
+struct nvc_ssd_spec {
+  int heads = 0, vdim = 0, state = 0, groups = 1, taps = 1, norm_groups = 1;
+};
+struct nvc_lightning_spec {
+  int heads = 0, dim = 0, vdim = 0;
+  std::vector<float> decay;  // per head
+};
+struct nvc_batatar_layer {
+  enum Kind { Parallel, Lightning } kind = Parallel;
+  nvc_chunk_attn_spec attn;        // left half of "parallel"
+  nvc_ssd_spec ssd;                // right half of "parallel"
+  nvc_lightning_spec lin;
+  nvc_routed_mlp_spec mlp;         // None or Moe (no identity experts, no clamp)
+};
+struct nvc_batatar_config {
+  int vocab = 0, width = 0;
+  float eps = 1e-5f;
+  float residual_mult = 1.f;
+  std::vector<nvc_batatar_layer> layers;
+  bool looped = false;             // config.json has `loop`: layers [loop_start, loop_stop) run loop_times passes
+  int loop_start = 0, loop_stop = 0, loop_times = 1;
+  struct Run { int layer; int pass; bool opens_pass; };
+  std::vector<Run> runs() const;
+  bool has_state() const { return !layers.empty(); }     // every mixer of the design keeps a recurrent state
+};
+
 struct nvc_model_config {
-  std::string architecture;   // "Qwen3ForCausalLM", "Karuzen", "Ranilix" or "Fefozen"
+  std::string architecture;   // "Qwen3ForCausalLM", "Karuzen", "Ranilix", "Fefozen" or "Batatar"
   nvc_qwen3_config qwen3{};
   int qwen3_tied = 0;
   nvc_karuzen_config karuzen;
   nvc_ranilix_config ranilix;
   nvc_fefozen_config fefozen;
+  nvc_batatar_config batatar;
 };

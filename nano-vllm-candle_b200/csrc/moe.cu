@@ -280,6 +280,19 @@ __global__ void moe_combine_f4_kernel(const float4* __restrict__ y, int ldy4, co
   }
 }
 
+// one CTA per (token, choice): the token's row times the pair's router weight, written where the sort put the pair
+template <typename T>
+__global__ void moe_scatter_scaled_kernel(const T* __restrict__ h, int ldh, const int32_t* __restrict__ pos, const float* __restrict__ topk_w,
+                                          T* __restrict__ out, int ldo, int top, int H) {
+  pdl_trigger();
+  pdl_wait();
+  const int pair = blockIdx.x, n = pair / top;
+  const float w = topk_w[pair];
+  const T* x = h + (int64_t)n * ldh;
+  T* y = out + (int64_t)pos[pair] * ldo;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) st_f(y + j, w * ld_f(x + j));
+}
+
 }  // namespace
 
 extern "C" {
@@ -401,6 +414,18 @@ int nvc_moe_combine_identity(nvc_ctx* ctx, const void* y, int y_dtype, int ldy, 
   else if (x_dtype == NVC_DT_F32) NVC_COMBINE(__nv_bfloat16, float);
   else NVC_COMBINE(__nv_bfloat16, __nv_bfloat16);
 #undef NVC_COMBINE
+  ctx->launches++;
+  return NVC_OK;
+}
+
+int nvc_moe_scatter_scaled(nvc_ctx* ctx, const void* h, int dtype, int ldh, const int32_t* pos, const float* topk_w, int top, void* out,
+                           int ldo, int N, int H, void* stream) {
+  NVC_REQUIRE(ctx, ctx && h && pos && topk_w && out, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, N >= 0 && H > 0 && top > 0 && ldh >= H && ldo >= H, NVC_EINVAL, "bad sizes");
+  if (N == 0) return NVC_OK;
+  NVC_DISPATCH_DT(dtype, T,
+                  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, moe_scatter_scaled_kernel<T>, dim3(N * top), dim3(H >= 1024 ? 256 : 128), 0, nvc_stream(stream),
+                                                 reinterpret_cast<const T*>(h), ldh, pos, topk_w, reinterpret_cast<T*>(out), ldo, top, H)));
   ctx->launches++;
   return NVC_OK;
 }

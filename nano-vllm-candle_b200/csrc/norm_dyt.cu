@@ -85,10 +85,11 @@ __global__ void latent_norm_store_kernel(const float* __restrict__ in, int ldi, 
 }
 
 // NVC_ACT_GELU_TANH_MUL: out[n, j] = gelu_tanh(in[n, j]) * in[n, Fp + j];  NVC_ACT_RELU2: out[n, j] = relu(in[n, j])^2;
-// NVC_ACT_GELU_TANH: gelu_tanh(in[n, j]);  NVC_ACT_GLU_CLAMP: g sigmoid(p1 g) (u + 1), g = min(in[n, j], p0), u = clamp(in[n, Fp + j], +-p0)
+// NVC_ACT_SILU_MUL: silu(in[n, j]) * in[n, Fp + j];  NVC_ACT_GELU_TANH: gelu_tanh(in[n, j]);  NVC_ACT_GLU_CLAMP: g sigmoid(p1 g) (u + 1), g = min(in[n, j], p0), u = clamp(in[n, Fp + j], +-p0)
 __device__ __forceinline__ float act_unit(int kind, float g, float u, float p0, float p1) {
   if (kind == NVC_ACT_GELU_TANH_MUL) return gelu_tanh_f32(g) * u;
   if (kind == NVC_ACT_GELU_TANH) return gelu_tanh_f32(g);
+  if (kind == NVC_ACT_SILU_MUL) return g * sigmoid_f32(g) * u;
   if (kind == NVC_ACT_GLU_CLAMP) {
     const float gc = fminf(g, p0);
     return gc * sigmoid_f32(p1 * gc) * (fminf(fmaxf(u, -p0), p0) + 1.0f);
@@ -104,7 +105,7 @@ __global__ void act_mul_kernel(const T* __restrict__ in, int ldi, T* __restrict_
                                float p1, int rows_per_cta) {
   pdl_trigger();
   pdl_wait();
-  const bool two = kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_GLU_CLAMP;
+  const bool two = kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_GLU_CLAMP || kind == NVC_ACT_SILU_MUL;
   for (int rr = 0; rr < rows_per_cta; ++rr) {
     const int64_t n = (int64_t)blockIdx.x * rows_per_cta + rr;
     if (n >= N) return;
@@ -197,7 +198,7 @@ int nvc_act_mul(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int d
 int nvc_act_mul_p(nvc_ctx* ctx, const void* in, int ldi, void* out, int ldo, int dtype, int N, int F, int Fp, int kind, float p0, float p1,
                   void* stream) {
   NVC_REQUIRE(ctx, ctx && in && out, NVC_EINVAL, "null pointer");
-  const bool two = kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_GLU_CLAMP;
+  const bool two = kind == NVC_ACT_GELU_TANH_MUL || kind == NVC_ACT_GLU_CLAMP || kind == NVC_ACT_SILU_MUL;
   NVC_REQUIRE(ctx, N >= 0 && F > 0 && (two || kind == NVC_ACT_RELU2 || kind == NVC_ACT_GELU_TANH), NVC_EINVAL, "bad arguments");
   NVC_REQUIRE(ctx, ldo >= F && ldi >= (two ? Fp + F : F), NVC_EINVAL, "bad strides");
   if (N == 0) return NVC_OK;

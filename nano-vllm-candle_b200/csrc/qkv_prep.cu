@@ -1,7 +1,8 @@
 // nvc_qkv_prep: everything between the fused q / k / v projection of a mixer and its attention or recurrence, in one pass
 // over the fp32 projection rows:
 //   + bias                                   (optional)
-//   per-head RMS norm of q and k             (optional; one weight vector of `dim` numbers shared by the heads)
+//   silu                                     (optional, on q, k and v)
+//   per-head RMS norm of q and k             (optional; one weight vector of `dim` numbers shared by the heads, or no weight)
 //   rotary positions on the first rot_dims numbers of every q / k head, pairs (2i, 2i + 1) or (i, i + rot_dims / 2),
 //                                            angles from a table of (cos, sin) per position
 //   k *= k_scale                             (after the rotation)
@@ -40,6 +41,7 @@ __global__ void qkv_prep_kernel(const PrepArgs a) {
     const float lam = p.blend == NVC_BLEND_MIX ? __ldg(p.lambda) : 0.f;
     for (int j = lane; j < p.vdim; j += 32) {
       float v = in[col + j] + (p.bias ? __ldg(p.bias + col + j) : 0.f);
+      if (p.act == NVC_PREP_ACT_SILU) v = v * sigmoid_f32(v);
       if (p.blend == NVC_BLEND_PROVIDE) p.v_first[(int64_t)n * p.ldvf + h * p.vdim + j] = v;
       else if (p.blend == NVC_BLEND_MIX) v = (1.0f - lam) * v + lam * p.v_first[(int64_t)n * p.ldvf + h * p.vdim + j];
       v *= p.v_scale;
@@ -54,13 +56,14 @@ __global__ void qkv_prep_kernel(const PrepArgs a) {
   if (orow < 0) return;
   float ss = 0.f;
   for (int j = lane; j < p.dim; j += 32) {
-    const float v = in[col + j] + (p.bias ? __ldg(p.bias + col + j) : 0.f);
+    float v = in[col + j] + (p.bias ? __ldg(p.bias + col + j) : 0.f);
+    if (p.act == NVC_PREP_ACT_SILU) v = v * sigmoid_f32(v);
     x[j] = v;
     ss += v * v;
   }
   const float* nw = is_q ? p.q_norm : p.k_norm;
   float r = 1.f;
-  if (nw) {
+  if (nw || p.unit_norm) {
     ss = warp_sum(ss);
     r = 1.0f / sqrtf(ss / (float)p.dim + p.eps);
   }
@@ -138,7 +141,8 @@ extern "C" int nvc_qkv_prep_run(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void
               NVC_EINVAL, "bad sizes");
   NVC_REQUIRE(ctx, p->rot_dims >= 0 && p->rot_dims % 2 == 0 && p->rot_dims <= p->dim && (p->rot_dims == 0 || (p->rot_table && p->positions)),
               NVC_EINVAL, "bad rotary arguments");
-  NVC_REQUIRE(ctx, (p->q_norm == nullptr) == (p->k_norm == nullptr), NVC_EINVAL, "q and k norms come together");
+  NVC_REQUIRE(ctx, (p->q_norm == nullptr) == (p->k_norm == nullptr) && !(p->unit_norm && p->q_norm), NVC_EINVAL,
+              "q and k norms come together, with a weight or without");
   NVC_REQUIRE(ctx, p->blend == NVC_BLEND_NONE || (p->v_first && p->ldvf >= p->kv_heads * p->vdim && (p->blend != NVC_BLEND_MIX || p->lambda)),
               NVC_EINVAL, "value blending needs its buffer and weight");
   NVC_REQUIRE(ctx, p->ldq >= p->q_heads * p->dim && p->ldk >= p->kv_heads * p->dim && p->ldv >= p->kv_heads * p->vdim, NVC_EINVAL,

@@ -15,6 +15,14 @@
 //                              S      <- decay^n S + sum_j decay^(n - 1 - j) k_j v_j^T n: tokens of the chunk
 //                            Powers of the decay come from a table built by repeated multiplication (exact for 0 and 1).
 // Both are plain fp32 FMA code; they differ from one another by rounding only.
+//
+// nvc_decay_scan is the same pair of kernels with what other linear recurrences of this shape need (VAR = true):
+//   a decay per token and head, given as its logarithm: S_t = exp(l_t) S_(t-1) + k_t v_t^T.  Inside a chunk only differences of the
+//     running sums L_t = l_0 + .. + l_t are exponentiated (all <= 0): A[t][j] carries exp(L_t - L_j), the state's share exp(L_t), the
+//     state update exp(L_(n-1) - L_j); a decay that underflows stays a plain zero;
+//   q and k heads shared by groups of value heads (head h reads q / k head h / (heads / qk_heads));
+//   a skip term o_t += skip_w[h] * skip_t.
+// A selective state space layer in its dual form is this recurrence with q = C, k = B, v = dt x, l = -exp(A_log) dt, skip = x.
 #include "typed.cuh"
 
 namespace {
@@ -25,11 +33,17 @@ struct RetArgs {
   int ldq, ldk, ldv, ldo;
   float* state;                  // [slots, heads, dim, vdim]
   const int32_t *state_slots, *cu_seqlens, *positions;
-  const float* decay;            // [heads]
+  const float* decay;            // [heads]                       (VAR = false)
   int heads, dim, vdim;
+  int qk_heads;                  // q / k heads (a divisor of heads)
+  const float* log_decay;        // [rows, ldl], one per head       (VAR = true)
+  int ldl;
+  const float* skip;             // [rows, lds] like v, or NULL
+  const float* skip_w;           // [heads]
+  int lds;
 };
 
-template <int DPT>
+template <int DPT, bool VAR>
 __global__ void retention_scan_kernel(const RetArgs a) {
   extern __shared__ float sm[];
   pdl_trigger();
@@ -40,7 +54,9 @@ __global__ void retention_scan_kernel(const RetArgs a) {
   float* q_s = sm;                    // [2][dim]
   float* k_s = sm + 2 * a.dim;        // [2][dim]
   float* red = sm + 4 * a.dim;        // [groups][32]
-  const float dec = __ldg(a.decay + h);
+  const int hq = h / (a.heads / a.qk_heads);
+  float dec = VAR ? 0.f : __ldg(a.decay + h);
+  const float sw = a.skip ? __ldg(a.skip_w + h) : 0.f;
   pdl_wait();
   const int r0 = a.cu_seqlens ? a.cu_seqlens[b] : b;
   const int r1 = a.cu_seqlens ? a.cu_seqlens[b + 1] : b + 1;
@@ -52,10 +68,11 @@ __global__ void retention_scan_kernel(const RetArgs a) {
   for (int i = 0; i < DPT; ++i) S[i] = (!fresh && vok && d0 + i < a.dim) ? sp[(int64_t)(d0 + i) * a.vdim + v] : 0.f;
   // stage token r0
   for (int d = threadIdx.x; d < a.dim; d += blockDim.x) {
-    q_s[d] = a.q[(int64_t)r0 * a.ldq + h * a.dim + d];
-    k_s[d] = a.k[(int64_t)r0 * a.ldk + h * a.dim + d];
+    q_s[d] = a.q[(int64_t)r0 * a.ldq + hq * a.dim + d];
+    k_s[d] = a.k[(int64_t)r0 * a.ldk + hq * a.dim + d];
   }
   float vt = vok ? a.v[(int64_t)r0 * a.ldv + h * a.vdim + v] : 0.f;
+  float ln = VAR ? a.log_decay[(int64_t)r0 * a.ldl + h] : 0.f;
   __syncthreads();
   for (int t = r0; t < r1; ++t) {
     const int cur = (t - r0) & 1;
@@ -64,11 +81,16 @@ __global__ void retention_scan_kernel(const RetArgs a) {
     float vn = 0.f;
     if (t + 1 < r1) {       // fetch the next token into the other buffer
       for (int d = threadIdx.x; d < a.dim; d += blockDim.x) {
-        q_s[(cur ^ 1) * a.dim + d] = a.q[(int64_t)(t + 1) * a.ldq + h * a.dim + d];
-        k_s[(cur ^ 1) * a.dim + d] = a.k[(int64_t)(t + 1) * a.ldk + h * a.dim + d];
+        q_s[(cur ^ 1) * a.dim + d] = a.q[(int64_t)(t + 1) * a.ldq + hq * a.dim + d];
+        k_s[(cur ^ 1) * a.dim + d] = a.k[(int64_t)(t + 1) * a.ldk + hq * a.dim + d];
       }
       vn = vok ? a.v[(int64_t)(t + 1) * a.ldv + h * a.vdim + v] : 0.f;
     }
+    if (VAR) {
+      dec = expf(ln);
+      if (t + 1 < r1) ln = a.log_decay[(int64_t)(t + 1) * a.ldl + h];
+    }
+    const float sk = (a.skip && vok) ? sw * a.skip[(int64_t)t * a.lds + h * a.vdim + v] : 0.f;
     float acc = 0.f;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
@@ -83,10 +105,10 @@ __global__ void retention_scan_kernel(const RetArgs a) {
       if (rg == 0) {
         float s = 0.f;
         for (int g = 0; g < groups; ++g) s += red[g * 32 + lane];
-        if (vok) a.o[(int64_t)t * a.ldo + h * a.vdim + v] = s;
+        if (vok) a.o[(int64_t)t * a.ldo + h * a.vdim + v] = s + sk;
       }
     } else if (vok) {
-      a.o[(int64_t)t * a.ldo + h * a.vdim + v] = acc;
+      a.o[(int64_t)t * a.ldo + h * a.vdim + v] = acc + sk;
     }
     vt = vn;
     __syncthreads();
@@ -112,7 +134,7 @@ __host__ __device__ inline int chunk_q_stride4(int dim) { const int q4 = (dim + 
 
 // Shared-memory operands are read as float4 (one load per four FMAs) and reused across a register tile: the kernel is bound
 // by the FMA pipe, not by shared-memory loads.
-template <int DPT>
+template <int DPT, bool VAR>
 __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const RetArgs a) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
@@ -126,9 +148,11 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
   float* v_s = reinterpret_cast<float*>(k_s + kChunk * q4);    // [32][32]
   float4* a_s = reinterpret_cast<float4*>(v_s + kChunk * 32);  // [32][9]    A[t][j], j in fours, zero above the diagonal
   float* part = reinterpret_cast<float*>(a_s + kChunk * 9);    // [warps][32][32]
-  float* gp = part + kChunkWarps * kChunk * 32;                // decay^0 .. decay^32
-  const float dec = __ldg(a.decay + h);
-  if (threadIdx.x == 0) {
+  float* gp = part + kChunkWarps * kChunk * 32;                // decay^0 .. decay^32;  VAR: the running sums L_0 .. L_31 of the chunk
+  const int hq = h / (a.heads / a.qk_heads);
+  const float sw = a.skip ? __ldg(a.skip_w + h) : 0.f;
+  if (!VAR && threadIdx.x == 0) {
+    const float dec = __ldg(a.decay + h);
     float p = 1.f;
     for (int i = 0; i <= kChunk; ++i) { gp[i] = p; p *= dec; }
   }
@@ -149,8 +173,17 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
     for (int idx = threadIdx.x; idx < kChunk * dim4; idx += blockDim.x) {
       const int t = idx / dim4, d = idx - t * dim4;
       const bool in = t < n && d < dim;
-      q_sf[t * 4 * RS + d] = in ? a.q[(int64_t)(c0 + t) * a.ldq + h * dim + d] : 0.f;
-      k_sf[t * dim4 + d] = in ? a.k[(int64_t)(c0 + t) * a.ldk + h * dim + d] : 0.f;
+      q_sf[t * 4 * RS + d] = in ? a.q[(int64_t)(c0 + t) * a.ldq + hq * dim + d] : 0.f;
+      k_sf[t * dim4 + d] = in ? a.k[(int64_t)(c0 + t) * a.ldk + hq * dim + d] : 0.f;
+    }
+    if (VAR && threadIdx.x < 32) {        // inclusive running sums of the chunk's log decays (a fixed order: lane by lane)
+      float l = lane < n ? a.log_decay[(int64_t)(c0 + lane) * a.ldl + h] : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, l, o);
+        if (lane >= o) l += up;
+      }
+      gp[lane] = l;
     }
     for (int idx = threadIdx.x; idx < kChunk * 32; idx += blockDim.x) {
       const int t = idx >> 5, c = idx & 31;
@@ -173,10 +206,18 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
       for (int g = 0; g < 2; ++g) {
         const int j0 = 4 * (w + 4 * g);
         float4 r;
+        if (VAR) {
+          const float Lt = gp[lane];
+          r.x = j0 <= lane ? acc[g][0] * expf(Lt - gp[j0]) : 0.f;
+          r.y = j0 + 1 <= lane ? acc[g][1] * expf(Lt - gp[j0 + 1]) : 0.f;
+          r.z = j0 + 2 <= lane ? acc[g][2] * expf(Lt - gp[j0 + 2]) : 0.f;
+          r.w = j0 + 3 <= lane ? acc[g][3] * expf(Lt - gp[j0 + 3]) : 0.f;
+        } else {
         r.x = j0 <= lane ? acc[g][0] * gp[lane - j0] : 0.f;
         r.y = j0 + 1 <= lane ? acc[g][1] * gp[lane - j0 - 1] : 0.f;
         r.z = j0 + 2 <= lane ? acc[g][2] * gp[lane - j0 - 2] : 0.f;
         r.w = j0 + 3 <= lane ? acc[g][3] * gp[lane - j0 - 3] : 0.f;
+        }
         a_s[lane * 9 + w + 4 * g] = r;
       }
     }
@@ -218,17 +259,18 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
           float cross = 0.f;
 #pragma unroll
           for (int g = 0; g < kChunkWarps; ++g) cross += part[(g * kChunk + t) * 32 + lane];
-          if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * a.vdim + v] = fmaf(gp[t + 1], cross, acc[tt]);
+          const float sk = (a.skip && vok) ? sw * a.skip[(int64_t)(c0 + t) * a.lds + h * a.vdim + v] : 0.f;
+          if (vok) a.o[(int64_t)(c0 + t) * a.ldo + h * a.vdim + v] = fmaf(VAR ? expf(gp[t]) : gp[t + 1], cross, acc[tt]) + sk;
         }
       }
     }
     // ---- the state after the chunk
     {
-      const float gn = gp[n];
+      const float gn = VAR ? expf(gp[n - 1]) : gp[n];
 #pragma unroll
       for (int i = 0; i < DPT; ++i) S[i] *= gn;
       for (int j = 0; j < n; ++j) {
-        const float vv = v_s[j * 32 + lane] * gp[n - 1 - j];
+        const float vv = v_s[j * 32 + lane] * (VAR ? expf(gp[n - 1] - gp[j]) : gp[n - 1 - j]);
 #pragma unroll
         for (int i4 = 0; i4 < DPT / 4; ++i4) {
           if (d0 + 4 * i4 < dim4) {
@@ -248,38 +290,32 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
       if (d0 + i < dim) sp[(int64_t)(d0 + i) * a.vdim + v] = S[i];
 }
 
-template <int DPT>
+template <int DPT, bool VAR>
 cudaError_t launch_chunk(nvc_ctx* ctx, const RetArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(retention_chunk_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(retention_chunk_kernel<DPT, VAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  return nvc_launch(ctx, retention_chunk_kernel<DPT>, grid, dim3(kChunkWarps * 32), smem, st, a);
+  return nvc_launch(ctx, retention_chunk_kernel<DPT, VAR>, grid, dim3(kChunkWarps * 32), smem, st, a);
 }
 
-}  // namespace
-
-extern "C" int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, float* o, int ldo,
-                                  float* state, const int32_t* state_slots, const int32_t* cu_seqlens, const int32_t* positions,
-                                  const float* decay, int B, int max_qlen, int heads, int dim, int vdim, void* stream) {
-  NVC_REQUIRE(ctx, ctx && q && k && v && o && state && state_slots && positions && decay, NVC_EINVAL, "null pointer");
-  NVC_REQUIRE(ctx, B > 0 && heads > 0 && dim > 0 && vdim > 0 && dim <= 1024 && heads <= 65535, NVC_EINVAL, "bad sizes");
-  NVC_REQUIRE(ctx, ldq >= heads * dim && ldk >= heads * dim && ldv >= heads * vdim && ldo >= heads * vdim, NVC_EINVAL, "bad strides");
-  RetArgs a{q, k, v, o, ldq, ldk, ldv, ldo, state, state_slots, cu_seqlens, positions, decay, heads, dim, vdim};
-  if (cu_seqlens && max_qlen > 4 && dim <= 512) {
+template <bool VAR>
+int run_scan(nvc_ctx* ctx, const RetArgs& a, int B, int max_qlen, void* stream) {
+  const int heads = a.heads, dim = a.dim, vdim = a.vdim;
+  if (a.cu_seqlens && max_qlen > 4 && dim <= 512) {
     // prompt portions: 32 tokens at a time
     const int per = ((dim + 3) / 4 * 4 + kChunkWarps - 1) / kChunkWarps;     // rows of the state per warp
     const dim3 grid(B, heads, (vdim + 31) / 32);
     const size_t smem = ((size_t)kChunk * 4 * chunk_q_stride4(dim) + (size_t)kChunk * 4 * ((dim + 3) / 4) + kChunk * 32 + kChunk * 36 +
                          kChunkWarps * kChunk * 32 + kChunk + 4) * sizeof(float);
     cudaError_t ce;
-    if (per <= 8) ce = launch_chunk<8>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (per <= 16) ce = launch_chunk<16>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (per <= 32) ce = launch_chunk<32>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (per <= 64) ce = launch_chunk<64>(ctx, a, grid, smem, nvc_stream(stream));
-    else ce = launch_chunk<128>(ctx, a, grid, smem, nvc_stream(stream));
+    if (per <= 8) ce = launch_chunk<8, VAR>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 16) ce = launch_chunk<16, VAR>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 32) ce = launch_chunk<32, VAR>(ctx, a, grid, smem, nvc_stream(stream));
+    else if (per <= 64) ce = launch_chunk<64, VAR>(ctx, a, grid, smem, nvc_stream(stream));
+    else ce = launch_chunk<128, VAR>(ctx, a, grid, smem, nvc_stream(stream));
     NVC_CUDA_CHECK(ctx, ce);
     ctx->launches++;
     return NVC_OK;
@@ -290,12 +326,38 @@ extern "C" int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const f
   const size_t smem = ((size_t)4 * dim + (size_t)groups * 32) * sizeof(float);
   cudaError_t ce;
   switch (dpt) {
-    case 16: ce = nvc_launch(ctx, retention_scan_kernel<16>, grid, block, smem, nvc_stream(stream), a); break;
-    case 32: ce = nvc_launch(ctx, retention_scan_kernel<32>, grid, block, smem, nvc_stream(stream), a); break;
-    case 64: ce = nvc_launch(ctx, retention_scan_kernel<64>, grid, block, smem, nvc_stream(stream), a); break;
-    default: ce = nvc_launch(ctx, retention_scan_kernel<128>, grid, block, smem, nvc_stream(stream), a); break;
+    case 16: ce = nvc_launch(ctx, retention_scan_kernel<16, VAR>, grid, block, smem, nvc_stream(stream), a); break;
+    case 32: ce = nvc_launch(ctx, retention_scan_kernel<32, VAR>, grid, block, smem, nvc_stream(stream), a); break;
+    case 64: ce = nvc_launch(ctx, retention_scan_kernel<64, VAR>, grid, block, smem, nvc_stream(stream), a); break;
+    default: ce = nvc_launch(ctx, retention_scan_kernel<128, VAR>, grid, block, smem, nvc_stream(stream), a); break;
   }
   NVC_CUDA_CHECK(ctx, ce);
   ctx->launches++;
   return NVC_OK;
+}
+
+}  // namespace
+
+extern "C" int nvc_retention_scan(nvc_ctx* ctx, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, float* o, int ldo,
+                                  float* state, const int32_t* state_slots, const int32_t* cu_seqlens, const int32_t* positions,
+                                  const float* decay, int B, int max_qlen, int heads, int dim, int vdim, void* stream) {
+  NVC_REQUIRE(ctx, ctx && q && k && v && o && state && state_slots && positions && decay, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, B > 0 && heads > 0 && dim > 0 && vdim > 0 && dim <= 1024 && heads <= 65535, NVC_EINVAL, "bad sizes");
+  NVC_REQUIRE(ctx, ldq >= heads * dim && ldk >= heads * dim && ldv >= heads * vdim && ldo >= heads * vdim, NVC_EINVAL, "bad strides");
+  RetArgs a{q, k, v, o, ldq, ldk, ldv, ldo, state, state_slots, cu_seqlens, positions, decay, heads, dim, vdim, heads, nullptr, 0, nullptr, nullptr, 0};
+  return run_scan<false>(ctx, a, B, max_qlen, stream);
+}
+
+extern "C" int nvc_decay_scan(nvc_ctx* ctx, const nvc_decay_scan_args* p, int B, int max_qlen, void* stream) {
+  NVC_REQUIRE(ctx, ctx && p && p->q && p->k && p->v && p->o && p->state && p->state_slots && p->positions, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, (p->decay != nullptr) != (p->log_decay != nullptr), NVC_EINVAL, "one of decay and log_decay");
+  NVC_REQUIRE(ctx, B > 0 && p->heads > 0 && p->qk_heads > 0 && p->heads % p->qk_heads == 0 && p->dim > 0 && p->vdim > 0 && p->dim <= 1024 &&
+                       p->heads <= 65535,
+              NVC_EINVAL, "bad sizes");
+  NVC_REQUIRE(ctx, p->ldq >= p->qk_heads * p->dim && p->ldk >= p->qk_heads * p->dim && p->ldv >= p->heads * p->vdim && p->ldo >= p->heads * p->vdim &&
+                       (!p->log_decay || p->ldl >= p->heads) && (!p->skip || (p->skip_w && p->lds >= p->heads * p->vdim)),
+              NVC_EINVAL, "bad strides");
+  RetArgs a{p->q, p->k, p->v, p->o, p->ldq, p->ldk, p->ldv, p->ldo, p->state, p->state_slots, p->cu_seqlens, p->positions, p->decay,
+            p->heads, p->dim, p->vdim, p->qk_heads, p->log_decay, p->ldl, p->skip, p->skip_w, p->lds};
+  return p->log_decay ? run_scan<true>(ctx, a, B, max_qlen, stream) : run_scan<false>(ctx, a, B, max_qlen, stream);
 }

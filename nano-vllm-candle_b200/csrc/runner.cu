@@ -1017,6 +1017,7 @@ extern "C" int nvc_runner_time_op(nvc_runner* r, int op, int iters, float* ms_pe
 nvc_model_body* nvc_make_karuzen_body(nvc_runner* r, const nvc_karuzen_config& cfg, int* status);   // model_karuzen.cu
 nvc_model_body* nvc_make_ranilix_body(nvc_runner* r, const nvc_ranilix_config& cfg, int* status);   // model_ranilix.cu
 nvc_model_body* nvc_make_fefozen_body(nvc_runner* r, const nvc_fefozen_config& cfg, int* status);   // model_fefozen.cu
+nvc_model_body* nvc_make_batatar_body(nvc_runner* r, const nvc_batatar_config& cfg, int* status);   // model_batatar.cu
 
 extern "C" int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_config* mc, const nvc_runner_options* opt,
                                              nvc_runner** out) {
@@ -1026,7 +1027,8 @@ extern "C" int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_confi
     NVC_REQUIRE(ctx, opt->dtype == NVC_DT_BF16, NVC_ENOTIMPL, "the Qwen3 body runs in bf16 only");
     return nvc_runner_create(ctx, &mc->qwen3, opt, out);
   }
-  NVC_REQUIRE(ctx, mc->architecture == "Karuzen" || mc->architecture == "Ranilix" || mc->architecture == "Fefozen", NVC_ENOTIMPL,
+  NVC_REQUIRE(ctx, mc->architecture == "Karuzen" || mc->architecture == "Ranilix" || mc->architecture == "Fefozen" || mc->architecture == "Batatar",
+              NVC_ENOTIMPL,
               "architecture " + mc->architecture + " has no model body");
   NVC_REQUIRE(ctx, ctx->tp_size == 1, NVC_ENOTIMPL, mc->architecture + " runs on one GPU");
   NVC_REQUIRE(ctx, opt->dtype == NVC_DT_BF16 || opt->dtype == NVC_DT_F32, NVC_EINVAL, "dtype must be NVC_DT_BF16 or NVC_DT_F32");
@@ -1046,6 +1048,7 @@ extern "C" int nvc_runner_create_from_config(nvc_ctx* ctx, const nvc_model_confi
   int rc = NVC_OK;
   if (mc->architecture == "Ranilix") r->body = nvc_make_ranilix_body(r, mc->ranilix, &rc);
   else if (mc->architecture == "Fefozen") r->body = nvc_make_fefozen_body(r, mc->fefozen, &rc);
+  else if (mc->architecture == "Batatar") r->body = nvc_make_batatar_body(r, mc->batatar, &rc);
   else r->body = nvc_make_karuzen_body(r, mc->karuzen, &rc);
   if (rc) return rc;
   r->V_l = r->body->vocab();

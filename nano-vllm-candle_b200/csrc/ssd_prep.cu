@@ -1,0 +1,135 @@
+// nvc_ssd_prep: a selective state space layer between its fused projection and its recurrence, over the new tokens of every sequence
+// of a step (fp32 throughout):
+//   channels [x | B | C]     causal convolution over time per channel with a bias, then silu.  The taps - 1 inputs in front of a
+//                            portion come from the sequence's convolution state (zeros for a sequence that starts at position 0)
+//   dt_h                     softplus(projection + dt_bias_h), no clamp
+//   outputs                  x, v = dt x (what the recurrence adds to the state, with B as its key), B, C,
+//                            log decay = -exp(A_log_h) dt   (the recurrence multiplies the state by its exponential)
+// nvc_ssd_conv_advance then writes every sequence's last taps - 1 inputs into its state slot (a portion shorter than that keeps the
+// tail of what the slot held).  It runs behind the first kernel on the same stream, which still reads the old state.
+// The recurrence itself is nvc_decay_scan (retention.cu) with q = C, k = B, a decay per token and head and the skip term D x.
+#include "typed.cuh"
+
+namespace {
+
+constexpr int kMaxTaps = 16;
+
+struct SsdArgs {
+  nvc_ssd_prep p;
+  int N;
+};
+
+__device__ __forceinline__ int ssd_find_seq(const int32_t* cu, int B, int row) {
+  int lo = 0, hi = B - 1;      // largest b with cu[b] <= row
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu[mid] <= row) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float softplus_f32(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+// thread = (token, channel); channels are the fast index, so a warp reads neighbouring columns of a projection row
+__global__ void ssd_prep_kernel(const SsdArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const nvc_ssd_prep& p = a.p;
+  const int inner = p.heads * p.vdim, gn = p.groups * p.state, C = inner + 2 * gn;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)a.N * C) return;
+  const int n = (int)(i / C), c = (int)(i % C);
+  int b = n, r0 = n;
+  if (p.cu_seqlens) {
+    b = ssd_find_seq(p.cu_seqlens, p.B, n);
+    r0 = p.cu_seqlens[b];
+  }
+  const int t = n - r0;                                  // index inside the portion
+  const bool fresh = p.positions[r0] == 0;
+  const float* st = p.conv_state + (int64_t)p.state_slots[b] * (p.taps - 1) * C;
+  float acc = __ldg(p.conv_b + c);
+  for (int i2 = 0; i2 < p.taps; ++i2) {
+    const int idx = t - (p.taps - 1) + i2;               // the input's index inside the portion; negative: in front of it
+    float x;
+    if (idx >= 0) x = p.in[(int64_t)(r0 + idx) * p.ldi + p.xbc_off + c];
+    else x = fresh ? 0.f : st[(int64_t)(p.taps - 1 + idx) * C + c];
+    acc = fmaf(__ldg(p.conv_w + (int64_t)i2 * C + c), x, acc);
+  }
+  const float y = acc * sigmoid_f32(acc);
+  if (c < inner) {
+    const int h = c / p.vdim;
+    const float dt = softplus_f32(p.in[(int64_t)n * p.ldi + p.dt_off + h] + __ldg(p.dt_bias + h));
+    p.x_out[(int64_t)n * p.ldx + c] = y;
+    p.v_out[(int64_t)n * p.ldx + c] = dt * y;
+    if (c == h * p.vdim) p.log_decay[(int64_t)n * p.ldl + h] = -expf(__ldg(p.A_log + h)) * dt;
+  } else if (c < inner + gn) {
+    p.b_out[(int64_t)n * p.ldbc + c - inner] = y;
+  } else {
+    p.c_out[(int64_t)n * p.ldbc + c - inner - gn] = y;
+  }
+}
+
+// thread = (sequence, channel): reads the taps - 1 inputs that end the sequence so far, then writes them
+__global__ void ssd_conv_advance_kernel(const SsdArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const nvc_ssd_prep& p = a.p;
+  const int C = p.heads * p.vdim + 2 * p.groups * p.state, keep = p.taps - 1;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)p.B * C) return;
+  const int b = (int)(i / C), c = (int)(i % C);
+  const int r0 = p.cu_seqlens ? p.cu_seqlens[b] : b;
+  const int r1 = p.cu_seqlens ? p.cu_seqlens[b + 1] : b + 1;
+  const int qlen = r1 - r0;
+  const bool fresh = p.positions[r0] == 0;
+  float* st = p.conv_state + (int64_t)p.state_slots[b] * keep * C;
+  float v[kMaxTaps];
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j) {
+    if (j < keep) {
+      const int idx = qlen - keep + j;
+      if (idx >= 0) v[j] = p.in[(int64_t)(r0 + idx) * p.ldi + p.xbc_off + c];
+      else v[j] = fresh ? 0.f : st[(int64_t)(keep + idx) * C + c];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j)
+    if (j < keep) st[(int64_t)j * C + c] = v[j];
+}
+
+int check(nvc_ctx* ctx, const nvc_ssd_prep* p) {
+  NVC_REQUIRE(ctx, ctx && p && p->in && p->conv_w && p->conv_b && p->conv_state && p->state_slots && p->positions, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, p->heads > 0 && p->vdim > 0 && p->groups > 0 && p->heads % p->groups == 0 && p->state > 0 && p->taps >= 1 && p->taps <= kMaxTaps &&
+                       p->B > 0,
+              NVC_EINVAL, "bad sizes (up to 16 taps)");
+  const int C = p->heads * p->vdim + 2 * p->groups * p->state;
+  NVC_REQUIRE(ctx, p->xbc_off >= 0 && p->dt_off >= 0 && p->ldi >= p->xbc_off + C && p->ldi >= p->dt_off + p->heads, NVC_EINVAL, "bad columns");
+  return NVC_OK;
+}
+
+}  // namespace
+
+extern "C" int nvc_ssd_prep_run(nvc_ctx* ctx, const nvc_ssd_prep* p, int N, void* stream) {
+  int rc = check(ctx, p);
+  if (rc) return rc;
+  NVC_REQUIRE(ctx, p->A_log && p->dt_bias && p->x_out && p->v_out && p->b_out && p->c_out && p->log_decay, NVC_EINVAL, "null pointer");
+  NVC_REQUIRE(ctx, N >= p->B && p->ldx >= p->heads * p->vdim && p->ldbc >= p->groups * p->state && p->ldl >= p->heads, NVC_EINVAL, "bad strides");
+  const int C = p->heads * p->vdim + 2 * p->groups * p->state;
+  SsdArgs a{*p, N};
+  const int64_t total = (int64_t)N * C;
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, ssd_prep_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, nvc_stream(stream), a));
+  ctx->launches++;
+  return NVC_OK;
+}
+
+extern "C" int nvc_ssd_conv_advance(nvc_ctx* ctx, const nvc_ssd_prep* p, void* stream) {
+  int rc = check(ctx, p);
+  if (rc) return rc;
+  if (p->taps == 1) return NVC_OK;
+  const int C = p->heads * p->vdim + 2 * p->groups * p->state;
+  SsdArgs a{*p, 0};
+  const int64_t total = (int64_t)p->B * C;
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, ssd_conv_advance_kernel, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, nvc_stream(stream), a));
+  ctx->launches++;
+  return NVC_OK;
+}
