@@ -126,6 +126,12 @@ def _declare(l: C.CDLL) -> None:
         "nvc_moe_combine_identity": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _vp],
         "nvc_delta_prep_run": [_vp, _vp, _i, _i, _vp],
         "nvc_delta_rule_scan": [_vp, _vp, _vp, _i, _vp, _i, _vp],
+        "nvc_rms_norm_blend": [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _f, _vp, _i, _i, _vp],
+        "nvc_group_norm_gate": [_vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+        "nvc_decay_scan": [_vp, _vp, _i, _i, _vp],
+        "nvc_ssd_prep_run": [_vp, _vp, _i, _vp],
+        "nvc_ssd_conv_advance": [_vp, _vp, _vp],
+        "nvc_moe_scatter_scaled": [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
         "nvc_debug_set": [_i, _i],
     }
     for name, args in sigs.items():

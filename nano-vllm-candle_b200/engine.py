@@ -337,7 +337,7 @@ class Qwen3ModelRunner:
 
 class ModelRunner(Qwen3ModelRunner):
     """A runner for any registered architecture, chosen by config.json (the model registry lives in the library:
-    "Qwen3ForCausalLM" -> the Qwen3 body, "Karuzen", "Ranilix" and "Fefozen" -> their bodies).  Same step methods as
+    "Qwen3ForCausalLM" -> the Qwen3 body, "Karuzen", "Ranilix", "Fefozen" and "Batatar" -> their bodies).  Same step methods as
     Qwen3ModelRunner; registry models attend through the paged cache, so their steps are `decode`
     and `step_mixed` (the engine drives them the same way).
 

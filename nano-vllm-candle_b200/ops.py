@@ -506,13 +506,15 @@ class QkvPrepC(C.Structure):
                 ("k_norm", C.c_void_p), ("eps", C.c_float), ("rot_dims", C.c_int), ("rot_half", C.c_int), ("rot_table", C.c_void_p),
                 ("positions", C.c_void_p), ("k_scale", C.c_float), ("blend", C.c_int), ("lambda_", C.c_void_p), ("v_first", C.c_void_p),
                 ("ldvf", C.c_int), ("q_out", C.c_void_p), ("ldq", C.c_int), ("k_out", C.c_void_p), ("v_out", C.c_void_p), ("ldk", C.c_int),
-                ("ldv", C.c_int), ("slot_mapping", C.c_void_p), ("q_dtype", C.c_int), ("kv_dtype", C.c_int), ("v_scale", C.c_float)]
+                ("ldv", C.c_int), ("slot_mapping", C.c_void_p), ("q_dtype", C.c_int), ("kv_dtype", C.c_int), ("v_scale", C.c_float),
+                ("unit_norm", C.c_int), ("act", C.c_int)]
 
 
 class AttnSpecC(C.Structure):
     """nvc_attn_spec of include/nvc_b200.h."""
     _fields_ = [("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("scale", C.c_float), ("window", C.c_int),
-                ("sink", C.c_void_p), ("gate", C.c_void_p), ("ldg", C.c_int), ("out_scale", C.c_float)]
+                ("sink", C.c_void_p), ("gate", C.c_void_p), ("ldg", C.c_int), ("out_scale", C.c_float), ("softcap", C.c_float),
+                ("chunk", C.c_int), ("gate_per_head", C.c_int)]
 
 
 def _a(t: Optional[torch.Tensor]):
@@ -556,21 +558,23 @@ def rotary_table(ctx, base: float, dims: int, max_pos: int, device="cuda:0"):
 
 def qkv_prep(ctx, x, q_off, k_off, v_off, q_heads, kv_heads, dim, vdim, q_out, k_out, v_out, *, bias=None, q_norm=None, k_norm=None,
              eps=1e-5, rot_dims=0, rot_half=False, rot_table=None, positions=None, k_scale=1.0, blend=0, lam=None, v_first=None,
-             slot_mapping=None, v_scale=1.0):
+             slot_mapping=None, v_scale=1.0, unit_norm=False, silu=False):
     """x: fp32 [N, ld] rows of a fused projection; q_out [N, q_heads * dim]; k_out / v_out: cache rows (slot_mapping) or [N, ...]."""
     p = QkvPrepC(_a(x), x.stride(0), _a(bias), q_off, k_off, v_off, q_heads, kv_heads, dim, vdim, _a(q_norm), _a(k_norm), eps, rot_dims,
                  1 if rot_half else 0, _a(rot_table), _a(positions), k_scale, blend, _a(lam), _a(v_first),
                  v_first.stride(0) if v_first is not None else 0, _a(q_out), q_out.stride(0), _a(k_out), _a(v_out), k_out.stride(0),
-                 v_out.stride(0), _a(slot_mapping), _dt(q_out), _dt(k_out), v_scale)
+                 v_out.stride(0), _a(slot_mapping), _dt(q_out), _dt(k_out), v_scale, 1 if unit_norm else 0, 1 if silu else 0)
     check(ctx.l.nvc_qkv_prep_run(ctx.h, C.byref(p), x.shape[0], _stream()), "nvc_qkv_prep_run", ctx.h)
 
 
 def attn_paged_wide(ctx, q, k_cache, v_cache, block_tables, context_lens, cu_seqlens, max_qlen: int, block_size: int, heads: int,
-                    kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0, sink=None, gate=None, out_scale: float = 1.0):
+                    kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0, sink=None, gate=None, out_scale: float = 1.0,
+                    softcap: float = 0.0, chunk: int = 0, gate_per_head: bool = False):
     """q: [rows, heads * dim]; k_cache [slots, kv_heads * dim], v_cache [slots, kv_heads * vdim]; returns [rows, heads * vdim]."""
     rows = q.shape[0]
     out = torch.empty(rows, heads * vdim, dtype=q.dtype, device=q.device)
-    sp = AttnSpecC(heads, kv_heads, dim, vdim, scale, window, _a(sink), _a(gate), gate.stride(0) if gate is not None else 0, out_scale)
+    sp = AttnSpecC(heads, kv_heads, dim, vdim, scale, window, _a(sink), _a(gate), gate.stride(0) if gate is not None else 0, out_scale,
+                   softcap, chunk, 1 if gate_per_head else 0)
     check(ctx.l.nvc_attn_paged_wide(ctx.h, _ptr(q), q.stride(0), _ptr(k_cache), k_cache.stride(0), _ptr(v_cache), v_cache.stride(0),
                                     _ptr(block_tables), block_tables.stride(0), _ptr(context_lens), _ptr(cu_seqlens), context_lens.numel(),
                                     rows, max_qlen, block_size, C.byref(sp), _ptr(out), out.stride(0), _dt(q), _stream()),
@@ -698,3 +702,86 @@ def delta_rule(ctx, x, offs, heads: int, kv_heads: int, dim: int, vdim: int, tap
     check(ctx.l.nvc_delta_prep_run(ctx.h, C.byref(p), N, longest, _stream()), "nvc_delta_prep_run", ctx.h)
     check(ctx.l.nvc_delta_rule_scan(ctx.h, C.byref(p), _ptr(o), o.stride(0), _ptr(state), max_qlen, _stream()), "nvc_delta_rule_scan", ctx.h)
     return o, q, k, v, gb
+
+
+# ---------------------------------------------------------------- blended norms, grouped gated norms, decayed scans, state space preparation
+ACT_SILU_MUL = 5
+
+
+class DecayScanC(C.Structure):
+    """nvc_decay_scan_args of include/nvc_b200.h."""
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ldq", C.c_int), ("ldk", C.c_int), ("ldv", C.c_int), ("o", C.c_void_p),
+                ("ldo", C.c_int), ("state", C.c_void_p), ("state_slots", C.c_void_p), ("cu_seqlens", C.c_void_p), ("positions", C.c_void_p),
+                ("decay", C.c_void_p), ("log_decay", C.c_void_p), ("ldl", C.c_int), ("skip", C.c_void_p), ("skip_w", C.c_void_p), ("lds", C.c_int),
+                ("heads", C.c_int), ("qk_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int)]
+
+
+class SsdPrepC(C.Structure):
+    """nvc_ssd_prep of include/nvc_b200.h."""
+    _fields_ = [("in_", C.c_void_p), ("ldi", C.c_int), ("xbc_off", C.c_int), ("dt_off", C.c_int), ("heads", C.c_int), ("vdim", C.c_int),
+                ("groups", C.c_int), ("state", C.c_int), ("taps", C.c_int), ("conv_w", C.c_void_p), ("conv_b", C.c_void_p),
+                ("conv_state", C.c_void_p), ("state_slots", C.c_void_p), ("cu_seqlens", C.c_void_p), ("positions", C.c_void_p),
+                ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("x_out", C.c_void_p), ("v_out", C.c_void_p), ("ldx", C.c_int),
+                ("b_out", C.c_void_p), ("c_out", C.c_void_p), ("ldbc", C.c_int), ("log_decay", C.c_void_p), ("ldl", C.c_int), ("B", C.c_int)]
+
+
+def rms_norm_blend(ctx, res, y0=None, w0=None, c0: float = 1.0, y1=None, w1=None, c1: float = 1.0, w=None, bias=None, eps: float = 1e-5,
+                   out_dtype=torch.float32, rows=None, write_back: bool = True, plain_out: bool = False):
+    """(residual after the sums - a new tensor, or None when rows gather or write_back is False; the normed rows - or the sum itself in
+    out_dtype when plain_out - or None)."""
+    ref = res if res is not None else y0
+    N = ref.shape[0] if rows is None else rows.numel()
+    H = ref.shape[1]
+    res_out = torch.empty_like(ref) if (rows is None and write_back) else None
+    out = torch.empty(N, H, dtype=out_dtype, device=ref.device) if (w is not None or plain_out) else None
+    check(ctx.l.nvc_rms_norm_blend(ctx.h, _ptr(res), _ptr(bias), _ptr(y0), _ptr(w0), c0, _ptr(y1), _ptr(w1), c1, _ptr(res_out), ref.stride(0),
+                                   _ptr(w), _ptr(out), 0 if out_dtype == torch.bfloat16 else 1, H, eps, _ptr(rows), N, H, _stream()),
+          "nvc_rms_norm_blend", ctx.h)
+    return res_out, out
+
+
+def group_norm_gate(ctx, o, gate, weight, groups: int, gsize: int, gate_first: bool, eps: float, act: str, out_dtype=torch.float32):
+    out = torch.empty(o.shape[0], groups * gsize, dtype=out_dtype, device=o.device)
+    check(ctx.l.nvc_group_norm_gate(ctx.h, _ptr(o), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight), _ptr(out),
+                                    out.stride(0), 0 if out_dtype == torch.bfloat16 else 1, groups, gsize, 1 if gate_first else 0, eps,
+                                    {"sigmoid": 0, "silu": 1}[act], o.shape[0], _stream()), "nvc_group_norm_gate", ctx.h)
+    return out
+
+
+def decay_scan(ctx, q, k, v, state, state_slots, cu_seqlens, positions, heads: int, qk_heads: int, dim: int, vdim: int, decay=None,
+               log_decay=None, skip=None, skip_w=None, max_qlen: int = 1 << 20):
+    """q, k: fp32 [N, qk_heads * dim]; v: fp32 [N, heads * vdim]; decay [heads] or log_decay [N, heads]; state updated in place."""
+    o = torch.empty(q.shape[0], heads * vdim, dtype=torch.float32, device=q.device)
+    p = DecayScanC(_a(q), _a(k), _a(v), q.stride(0), k.stride(0), v.stride(0), _a(o), o.stride(0), _a(state), _a(state_slots), _a(cu_seqlens),
+                   _a(positions), _a(decay), _a(log_decay), log_decay.stride(0) if log_decay is not None else 0, _a(skip), _a(skip_w),
+                   skip.stride(0) if skip is not None else 0, heads, qk_heads, dim, vdim)
+    check(ctx.l.nvc_decay_scan(ctx.h, C.byref(p), state_slots.numel(), max_qlen, _stream()), "nvc_decay_scan", ctx.h)
+    return o
+
+
+def ssd_prep(ctx, x, xbc_off: int, dt_off: int, heads: int, vdim: int, groups: int, state: int, taps: int, conv_w, conv_b, conv_state,
+             state_slots, cu_seqlens, positions, A_log, dt_bias):
+    """x: fp32 [N, ld] rows of the fused projection; conv_w [taps, C] tap-major; conv_state [slots, taps - 1, C] is advanced in place.
+    Returns (x, v = dt x, B, C, log_decay)."""
+    N, dev = x.shape[0], x.device
+    inner, gn = heads * vdim, groups * state
+    xo = torch.empty(N, inner, dtype=torch.float32, device=dev)
+    vo = torch.empty_like(xo)
+    bo = torch.empty(N, gn, dtype=torch.float32, device=dev)
+    co = torch.empty_like(bo)
+    ld = torch.empty(N, heads, dtype=torch.float32, device=dev)
+    p = SsdPrepC(_a(x), x.stride(0), xbc_off, dt_off, heads, vdim, groups, state, taps, _a(conv_w), _a(conv_b), _a(conv_state), _a(state_slots),
+                 _a(cu_seqlens), _a(positions), _a(A_log), _a(dt_bias), _a(xo), _a(vo), inner, _a(bo), _a(co), gn, _a(ld), heads,
+                 state_slots.numel())
+    check(ctx.l.nvc_ssd_prep_run(ctx.h, C.byref(p), N, _stream()), "nvc_ssd_prep_run", ctx.h)
+    check(ctx.l.nvc_ssd_conv_advance(ctx.h, C.byref(p), _stream()), "nvc_ssd_conv_advance", ctx.h)
+    return xo, vo, bo, co, ld
+
+
+def moe_scatter_scaled(ctx, h, pos, w, rows: int):
+    """out[pos[n * top + t]] = w[n, t] * h[n]; `rows` rows of output (zeros elsewhere)."""
+    N, top = w.shape
+    out = torch.zeros(rows, h.shape[1], dtype=h.dtype, device=h.device)
+    check(ctx.l.nvc_moe_scatter_scaled(ctx.h, _ptr(h), _dt(h), h.stride(0), _ptr(pos), _ptr(w), top, _ptr(out), out.stride(0), N, h.shape[1],
+                                       _stream()), "nvc_moe_scatter_scaled", ctx.h)
+    return out

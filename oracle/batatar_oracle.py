@@ -32,7 +32,6 @@ CPU; nothing is shared with the CUDA path.
 """
 from __future__ import annotations
 
-import math
 from typing import Dict, List, Optional
 
 import torch
@@ -51,9 +50,10 @@ def silu(z: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------ chunked attention
 
 def chunk_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: float, pos0: int, keys: torch.Tensor,
-                    values: torch.Tensor):
+                    values: torch.Tensor, sink: bool = True):
     """h [T, W] at positions pos0 ..; keys [P, G, d] (already unit-rms) and values [P, G, vd] of the tokens before.
-    Returns (out [T, W], keys [P + T, G, d], values [P + T, G, vd])."""
+    Returns (out [T, W], keys [P + T, G, d], values [P + T, G, vd]).  sink = False leaves the design (tests use it to show that
+    the sink matters)."""
     T = h.shape[0]
     H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ p["q"].T + p["q.b"]).view(T, H, d)
@@ -74,7 +74,7 @@ def chunk_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: f
             if cap:
                 s = cap * torch.tanh(s / cap)
             e = torch.exp(s.double())
-            w = (e / (1.0 + e.sum())).float()               # the sink: one more term exp(0) that carries no value
+            w = (e / ((1.0 if sink else 0.0) + e.sum())).float()     # the sink: one more term exp(0) that carries no value
             out[t, hh] = (w.view(-1, 1) * values[lo: i + 1, g]).sum(0) * gate[t, hh]
     return out.reshape(T, H * vd) @ p["o"].T, keys, values
 
@@ -196,8 +196,9 @@ def layer_runs(cfg: dict) -> List[tuple]:
 class Batatar:
     """The whole model over explicit per-request caches.  cfg: the dict of config.json; params: name -> tensor."""
 
-    def __init__(self, cfg: dict, params: Dict[str, torch.Tensor]):
+    def __init__(self, cfg: dict, params: Dict[str, torch.Tensor], sink: bool = True):
         self.cfg = cfg
+        self.sink = sink
         self.p = {k: v.float() for k, v in params.items()}
         self.eps = cfg["norm"]["eps"]
 
@@ -224,7 +225,7 @@ class Batatar:
                 ml = m["left"]
                 empty = (torch.zeros(0, ml["kv_heads"], ml["dim"]), torch.zeros(0, ml["kv_heads"], ml["vdim"]))
                 ks, vs = cache["kv"].get(key, empty)
-                left, ks, vs = chunk_attention(h, sub(mp, "left."), ml, eps, pos0, ks, vs)
+                left, ks, vs = chunk_attention(h, sub(mp, "left."), ml, eps, pos0, ks, vs, self.sink)
                 cache["kv"][key] = (ks, vs)
                 right, cache["state"][key] = ssd_mixer(h, sub(mp, "right."), m["right"], eps, cache["state"].get(key))
                 y = 0.5 * (rms_norm(left, mp["left.out"], eps) + rms_norm(right, mp["right.out"], eps))
