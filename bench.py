@@ -560,7 +560,7 @@ def main():
     ap.add_argument("--compare-families", action="store_true",
                     help="instead of the headline workload: a registry family (--compare-family) beside Qwen3 at equal layer sizes (prefill / decode throughput, "
                          "per-op rooflines), one JSON line; 1 GPU")
-    ap.add_argument("--compare-family", default="karuzen", choices=["karuzen", "ranilix", "fefozen"],
+    ap.add_argument("--compare-family", default="karuzen", choices=["karuzen", "ranilix", "fefozen", "batatar"],
                     help="with --compare-families: which registry family stands beside Qwen3")
     ap.add_argument("--compare-sizes", default="", help="with --compare-families: comma-separated size names (default: all)")
     args = ap.parse_args()

@@ -1,4 +1,4 @@
-"""Karuzen, Ranilix or Fefozen beside the closest existing family (Qwen3, dense GQA) at equal layer sizes: prefill and decode throughput
+"""Karuzen, Ranilix, Fefozen or Batatar beside the closest existing family (Qwen3, dense GQA) at equal layer sizes: prefill and decode throughput
 through LLMEngine, plus per-op times and roofline fractions.  Random weights, synthetic prompts.  Used by
 `bench.py --compare-families`; the default benchmark does not touch this module.
 
@@ -329,6 +329,136 @@ def fefozen_rooflines(cfg, prof: Dict[str, float], N: int, B: int, ctx_lens: Lis
     return out
 
 
+# ---- Batatar at the same sizes: four layers - chunked capped attention beside a selective state space layer (twice the width inside,
+# heads of 64 numbers over states of 128), lightning attention (heads of 128 x 128), lightning attention, the parallel mixer again - with
+# sigmoid-routed experts of ff / 2 hidden units, top 2 of 16 (the gated feed-forward's active parameter count), behind every mixer; layers
+# 1 and 2 form a looped block of ONE pass, so that the product that opens a pass is part of the step.
+B_CHUNK = 256
+
+
+def batatar_config(sz: dict) -> dict:
+    H, W = sz["heads"], sz["width"]
+    par = {"left": {"heads": H, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0, "mask": {"size": B_CHUNK}},
+           "right": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4, "norm_groups": 2}}
+    lin = {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3 - 6 * i / max(1, H - 1)) for i in range(H)]}
+    mlp = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": sz["ff"] // 2}}
+    kinds = ["parallel", "lightning", "lightning", "parallel"]
+    layers = [{"type": kinds[i % 4], "mixer": dict(par if kinds[i % 4] == "parallel" else lin), "mlp": dict(mlp)} for i in range(sz["layers"])]
+    return {"architecture": "Batatar", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "loop": {"start": 1, "stop": min(3, sz["layers"]), "times": 1}, "layers": layers}
+
+
+def batatar_weights(cfg: dict, seed: int = 0):
+    """(name, bf16 CPU tensor) pairs, generated one at a time."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g) * i ** -0.5).bfloat16()
+
+    yield "embed", (torch.randn(cfg["vocab"], W, generator=g)).bfloat16()
+    yield "head", mat(cfg["vocab"], W)
+    yield "final.norm", torch.ones(W).bfloat16()
+    if cfg.get("loop"):
+        yield "loop.in", mat(W, 2 * W)
+        yield "loop.step", torch.zeros(cfg["loop"]["times"], W).bfloat16()
+    for i, ly in enumerate(cfg["layers"]):
+        m, p = ly["mixer"], f"l{i}."
+        yield p + "norm1", torch.ones(W).bfloat16()
+        yield p + "norm2", torch.ones(W).bfloat16()
+        if ly["type"] == "parallel":
+            a, b = m["left"], m["right"]
+            H, G, d, vd = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            for n, rows in (("q", H * d), ("k", G * d), ("v", G * vd)):
+                yield p + "mix.left." + n, mat(rows, W)
+                yield p + "mix.left." + n + ".b", torch.zeros(rows).bfloat16()
+            yield p + "mix.left.g", mat(H, W)
+            yield p + "mix.left.o", mat(W, H * vd)
+            yield p + "mix.left.out", torch.ones(W).bfloat16()
+            Hs, vs, N, Gs, taps = b["heads"], b["vdim"], b["state"], b["groups"], b["conv"]
+            inner, C = Hs * vs, Hs * vs + 2 * Gs * N
+            yield p + "mix.right.in", mat(2 * inner + 2 * Gs * N + Hs, W)
+            yield p + "mix.right.conv", (torch.randn(C, taps, generator=g) * 0.5).bfloat16()
+            yield p + "mix.right.conv.b", torch.zeros(C).bfloat16()
+            yield p + "mix.right.dt_bias", torch.zeros(Hs).bfloat16()
+            yield p + "mix.right.A_log", torch.zeros(Hs).bfloat16()
+            yield p + "mix.right.D", torch.ones(Hs).bfloat16()
+            yield p + "mix.right.norm", torch.ones(inner).bfloat16()
+            yield p + "mix.right.o", mat(W, inner)
+            yield p + "mix.right.out", torch.ones(W).bfloat16()
+        else:
+            H, d, vd = m["heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", H * d), ("k", H * d), ("v", H * vd), ("g", H * vd)):
+                yield p + "mix." + n, mat(rows, W)
+            yield p + "mix.norm", torch.ones(H * vd).bfloat16()
+            yield p + "mix.o", mat(W, H * vd)
+        f = ly["mlp"]
+        E, ef = f["router"]["experts"], f["expert"]["ff"]
+        yield p + "mlp.router", mat(E, W)
+        for e in range(E):
+            yield p + f"mlp.e{e}.gate", mat(ef, W)
+            yield p + f"mlp.e{e}.up", mat(ef, W)
+            yield p + f"mlp.e{e}.down", mat(W, ef)
+
+
+def batatar_rooflines(cfg, prof: Dict[str, float], N: int, B: int, ctx_lens: List[int], q_lens: List[int], pk) -> dict:
+    """Per-op roofline of one profiled step: the times are sums over the layer runs, the work is summed the same way.  Both recurrences
+    run on the fp32 FMA pipe (their state is fp32): their fractions are against that pipe's peak (pk["fp32"]); 4 N H d vd flops is the
+    token-by-token form's count (state update and read-out), as for the retention scan of the Ranilix family."""
+    W = cfg["width"]
+    names = ("gemm_in", "gemm_o", "gemm_loop", "attention", "ssd_scan", "lightning_scan", "moe_gate_up", "moe_down")
+    work = {k: [0.0, 0.0] for k in names}
+
+    def add(name, flops, nbytes):
+        work[name][0] += flops
+        work[name][1] += nbytes
+
+    for ly in cfg["layers"]:
+        m, f = ly["mixer"], ly["mlp"]
+        if ly["type"] == "parallel":
+            a, b = m["left"], m["right"]
+            H, G, d, vd, size = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["mask"]["size"]
+            Hs, vs, Ns, Gs = b["heads"], b["vdim"], b["state"], b["groups"]
+            inner = Hs * vs
+            n_in = H * d + G * (d + vd) + H + 2 * inner + 2 * Gs * Ns + Hs
+            n_o = H * vd + inner
+            pairs, keys = 0, 0
+            for q, c in zip(q_lens, ctx_lens):
+                for t in range(c - q, c):
+                    pairs += t % size + 1
+                keys += min(c, q + (c - q) % size)
+            add("attention", 2.0 * pairs * H * (d + vd), 2.0 * (keys * G * (d + vd) + N * H * (d + vd)))
+            add("ssd_scan", 4.0 * N * Hs * Ns * vs, 4.0 * (N * (2 * Gs * Ns + 3 * inner) + 2 * B * Hs * Ns * vs))
+        else:
+            H, d, vd = m["heads"], m["dim"], m["vdim"]
+            n_in, n_o = 2 * H * d + 2 * H * vd, H * vd
+            add("lightning_scan", 4.0 * N * H * d * vd, 4.0 * (N * H * (2 * d + 2 * vd) + 2 * B * H * d * vd))
+        add("gemm_in", 2.0 * N * n_in * W, 2.0 * n_in * W + 2.0 * N * W + 4.0 * N * n_in)
+        add("gemm_o", 2.0 * N * n_o * W, 2.0 * n_o * W + 2.0 * N * n_o + 4.0 * N * W * (2 if ly["type"] == "parallel" else 1))
+        E, top, ef = f["router"]["experts"], f["router"]["top"], f["expert"]["ff"]
+        touched = min(E, N * top)
+        add("moe_gate_up", 4.0 * N * top * ef * W, 2.0 * (2 * touched * ef * W + N * top * (2 * ef + W)))
+        add("moe_down", 2.0 * N * top * ef * W, 2.0 * (touched * ef * W + N * top * ef) + 4.0 * N * top * W)
+    if cfg.get("loop"):
+        t = cfg["loop"]["times"]
+        add("gemm_loop", t * 4.0 * N * W * W, t * (4.0 * W * W + 4.0 * N * W + 4.0 * N * W))
+    out = {}
+    for name, (fl, by) in work.items():
+        if name in prof and fl > 0:
+            if name in ("ssd_scan", "lightning_scan"):
+                tmin = max(fl / (pk.get("fp32", 70.0) * 1e12), by / (pk["hbm"] * 1e9)) * 1e6
+                out[name] = {"us": round(prof[name], 2), "fp32_tflops": round(fl / prof[name] / 1e6, 2), "gbs": round(by / prof[name] / 1e3, 1),
+                             "roofline_frac": round(tmin / prof[name], 3)}
+            else:
+                out[name] = _roof(fl, by, prof[name], pk)
+    for name in ("norm", "loop_concat", "qkv_prep", "ssd_prep", "ssd_gate_norm", "lightning_prep", "lightning_norm_gate", "moe_route", "moe_sort",
+                 "moe_scatter", "moe_glu", "moe_combine", "embed", "final_norm", "lm_head"):
+        if name in prof:
+            out[name] = {"us": round(prof[name], 2)}
+    return out
+
+
 def _prompts(n, length, vocab, seed):
     rng = np.random.default_rng(seed)
     return [rng.integers(0, vocab, length).tolist() for _ in range(n)]
@@ -408,7 +538,8 @@ def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, p
     pk = peaks or {"bf16": 1590.0, "hbm": 6650.0, "source": "fallback"}
     make_config, make_weights, rooflines = {"karuzen": (karuzen_config, karuzen_weights, karuzen_rooflines),
                                             "ranilix": (ranilix_config, ranilix_weights, ranilix_rooflines),
-                                            "fefozen": (fefozen_config, fefozen_weights, fefozen_rooflines)}[family]
+                                            "fefozen": (fefozen_config, fefozen_weights, fefozen_rooflines),
+                                            "batatar": (batatar_config, batatar_weights, batatar_rooflines)}[family]
     T = batch_p * plen
     nblocks = max(batch_p, batch_d) * (-(-(plen + W + K + 24) // BLOCK)) + 8
     results = []
@@ -416,6 +547,8 @@ def compare(ctx_ours, sizes=None, batch_p=16, batch_d=64, plen=512, K=32, W=4, p
         rec = {"size": sz["name"]}
         if family == "ranilix" and "moe" in sz:
             continue                                               # the design has no mixture of experts
+        if family == "batatar" and "moe" in sz:
+            continue                                               # every size of this family already has experts
         # ---- the registry family
         cfg = make_config(sz)
         t0 = time.perf_counter()

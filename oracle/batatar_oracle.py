@@ -49,6 +49,28 @@ def silu(z: torch.Tensor) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------ chunked attention
 
+def capped_chunk_softmax(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, pos0: int, scale: float, cap: float, size: int,
+                         sink: bool = True) -> torch.Tensor:
+    """q [T, H, d] at positions pos0 ..; keys [pos0 + T, G, d], values [pos0 + T, G, vd] of every token so far.
+    Returns [T, H, vd]: s = cap tanh(scale (q . k) / cap) (cap 0: not capped); keys j <= i of the query's own chunk
+    (floor(i / size) = floor(j / size); size 0: all); p_j = exp(s_j) / (1 + sum exp(s_j))."""
+    T, H, _ = q.shape
+    G = keys.shape[1]
+    out = torch.zeros(T, H, values.shape[2])
+    for t in range(T):
+        i = pos0 + t
+        lo = (i // size) * size if size else 0
+        for hh in range(H):
+            g = hh // (H // G)
+            s = (keys[lo: i + 1, g] @ q[t, hh]) * scale
+            if cap:
+                s = cap * torch.tanh(s / cap)
+            e = torch.exp(s.double())
+            w = (e / ((1.0 if sink else 0.0) + e.sum())).float()     # the sink: one more term exp(0) that carries no value
+            out[t, hh] = (w.view(-1, 1) * values[lo: i + 1, g]).sum(0)
+    return out
+
+
 def chunk_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: float, pos0: int, keys: torch.Tensor,
                     values: torch.Tensor, sink: bool = True):
     """h [T, W] at positions pos0 ..; keys [P, G, d] (already unit-rms) and values [P, G, vd] of the tokens before.
@@ -61,21 +83,9 @@ def chunk_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: f
     v = (h @ p["v"].T + p["v.b"]).view(T, G, vd)
     q, k = rms_norm(q, None, eps), rms_norm(k, None, eps)
     keys, values = torch.cat([keys, k], 0), torch.cat([values, v], 0)
-    gate = torch.sigmoid(h @ p["g"].T)                      # [T, H]
+    gate = torch.sigmoid(h @ p["g"].T)                      # [T, H]: one number per head
     size = (m.get("mask") or {}).get("size", 0)
-    cap = m.get("softcap", 0.0)
-    out = torch.zeros(T, H, vd)
-    for t in range(T):
-        i = pos0 + t
-        lo = (i // size) * size if size else 0
-        for hh in range(H):
-            g = hh // (H // G)
-            s = (keys[lo: i + 1, g] @ q[t, hh]) * m["scale"]
-            if cap:
-                s = cap * torch.tanh(s / cap)
-            e = torch.exp(s.double())
-            w = (e / ((1.0 if sink else 0.0) + e.sum())).float()     # the sink: one more term exp(0) that carries no value
-            out[t, hh] = (w.view(-1, 1) * values[lo: i + 1, g]).sum(0) * gate[t, hh]
+    out = capped_chunk_softmax(q, keys, values, pos0, m["scale"], m.get("softcap", 0.0), size, sink) * gate.unsqueeze(-1)
     return out.reshape(T, H * vd) @ p["o"].T, keys, values
 
 
