@@ -6,7 +6,7 @@
 // k and scaled k).
 //
 // Two kernels, both with one CTA per (sequence, head, slice of 32 value columns) whose threads (column v, row group r) keep rows
-// [r DPT, (r + 1) DPT) of column v of the state in registers:
+// [r DPT, (r + 1) DPT) of column v of the state in registers (token by token: 32 rows per warp, up to 32 warps):
 //   retention_scan_kernel    token by token (decode steps and very short portions): 2 DPT FMAs per thread and token and, when the
 //                            rows are split, one shared-memory reduction; the next token's q / k / v are fetched meanwhile.
 //   retention_chunk_kernel   32 tokens at a time (prompt portions), the same recurrence regrouped:
@@ -320,17 +320,15 @@ int run_scan(nvc_ctx* ctx, const RetArgs& a, int B, int max_qlen, void* stream) 
     ctx->launches++;
     return NVC_OK;
   }
-  const int dpt = dim <= 16 ? 16 : (dim <= 32 ? 32 : (dim <= 64 ? 64 : 128));
+  // rows of a state column are split over warps of the CTA, 32 (16) rows each: a decode step is bound by reading and writing the
+  // state once, and a CTA of one warp holding whole columns of 128 numbers leaves too few loads in flight
+  const int dpt = dim <= 16 ? 16 : 32;
   const int groups = (dim + dpt - 1) / dpt;
   const dim3 grid(B, heads, (vdim + 31) / 32), block(32 * groups);
   const size_t smem = ((size_t)4 * dim + (size_t)groups * 32) * sizeof(float);
   cudaError_t ce;
-  switch (dpt) {
-    case 16: ce = nvc_launch(ctx, retention_scan_kernel<16, VAR>, grid, block, smem, nvc_stream(stream), a); break;
-    case 32: ce = nvc_launch(ctx, retention_scan_kernel<32, VAR>, grid, block, smem, nvc_stream(stream), a); break;
-    case 64: ce = nvc_launch(ctx, retention_scan_kernel<64, VAR>, grid, block, smem, nvc_stream(stream), a); break;
-    default: ce = nvc_launch(ctx, retention_scan_kernel<128, VAR>, grid, block, smem, nvc_stream(stream), a); break;
-  }
+  if (dpt == 16) ce = nvc_launch(ctx, retention_scan_kernel<16, VAR>, grid, block, smem, nvc_stream(stream), a);
+  else ce = nvc_launch(ctx, retention_scan_kernel<32, VAR>, grid, block, smem, nvc_stream(stream), a);
   NVC_CUDA_CHECK(ctx, ce);
   ctx->launches++;
   return NVC_OK;
