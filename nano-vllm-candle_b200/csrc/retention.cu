@@ -120,7 +120,8 @@ __global__ void retention_scan_kernel(const RetArgs a) {
 }
 
 constexpr int kChunk = 32;          // tokens per chunk
-constexpr int kChunkWarps = 4;
+constexpr int kChunkWarps = 8;         // a divisor of 8: the chunk's 8 groups of four keys are dealt out to the warps
+constexpr int kKeyGroups = 8 / kChunkWarps;
 
 __device__ __forceinline__ float dot4(const float4& x, const float4& y, float acc) {
   acc = fmaf(x.x, y.x, acc);
@@ -134,8 +135,10 @@ __host__ __device__ inline int chunk_q_stride4(int dim) { const int q4 = (dim + 
 
 // Shared-memory operands are read as float4 (one load per four FMAs) and reused across a register tile: the kernel is bound
 // by the FMA pipe, not by shared-memory loads.
+// The variant with per-token decays at up to 16 rows per warp is capped at 85 registers (a few spilled words) so that three CTAs -
+// what shared memory allows - fit an SM; the fixed-decay variant needs 80 as it is.
 template <int DPT, bool VAR>
-__global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const RetArgs a) {
+__global__ void __launch_bounds__(kChunkWarps * 32, (VAR && DPT <= 16) ? 3 : 1) retention_chunk_kernel(const RetArgs a) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
@@ -190,21 +193,21 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
       v_s[idx] = (t < n && v0 + c < a.vdim) ? a.v[(int64_t)(c0 + t) * a.ldv + h * a.vdim + v0 + c] : 0.f;
     }
     __syncthreads();
-    // ---- A[t][j]: lane = t; warp w takes the groups of four keys jg = w and w + 4 (j = 4 jg + u)
+    // ---- A[t][j]: lane = t; warp w takes the groups of four keys jg = w, w + warps, ... (j = 4 jg + u)
     {
-      float acc[2][4];
+      float acc[kKeyGroups][4];
 #pragma unroll
-      for (int g = 0; g < 2; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+      for (int g = 0; g < kKeyGroups; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
       for (int d4 = 0; d4 < q4; ++d4) {
         const float4 qv = q_s[lane * RS + d4];
 #pragma unroll
-        for (int g = 0; g < 2; ++g)
+        for (int g = 0; g < kKeyGroups; ++g)
 #pragma unroll
-          for (int u = 0; u < 4; ++u) acc[g][u] = dot4(qv, k_s[(4 * (w + 4 * g) + u) * q4 + d4], acc[g][u]);
+          for (int u = 0; u < 4; ++u) acc[g][u] = dot4(qv, k_s[(4 * (w + kChunkWarps * g) + u) * q4 + d4], acc[g][u]);
       }
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        const int j0 = 4 * (w + 4 * g);
+      for (int g = 0; g < kKeyGroups; ++g) {
+        const int j0 = 4 * (w + kChunkWarps * g);
         float4 r;
         if (VAR) {
           const float Lt = gp[lane];
@@ -213,12 +216,12 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
           r.z = j0 + 2 <= lane ? acc[g][2] * expf(Lt - gp[j0 + 2]) : 0.f;
           r.w = j0 + 3 <= lane ? acc[g][3] * expf(Lt - gp[j0 + 3]) : 0.f;
         } else {
-        r.x = j0 <= lane ? acc[g][0] * gp[lane - j0] : 0.f;
-        r.y = j0 + 1 <= lane ? acc[g][1] * gp[lane - j0 - 1] : 0.f;
-        r.z = j0 + 2 <= lane ? acc[g][2] * gp[lane - j0 - 2] : 0.f;
-        r.w = j0 + 3 <= lane ? acc[g][3] * gp[lane - j0 - 3] : 0.f;
+          r.x = j0 <= lane ? acc[g][0] * gp[lane - j0] : 0.f;
+          r.y = j0 + 1 <= lane ? acc[g][1] * gp[lane - j0 - 1] : 0.f;
+          r.z = j0 + 2 <= lane ? acc[g][2] * gp[lane - j0 - 2] : 0.f;
+          r.w = j0 + 3 <= lane ? acc[g][3] * gp[lane - j0 - 3] : 0.f;
         }
-        a_s[lane * 9 + w + 4 * g] = r;
+        a_s[lane * 9 + w + kChunkWarps * g] = r;
       }
     }
     // ---- the state's share of every output: this warp's rows of S against q_t, lane = value column
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(kChunkWarps * 32) retention_chunk_kernel(const
       part[(w * kChunk + t) * 32 + lane] = acc;
     }
     __syncthreads();
-    // ---- o_t for this warp's tokens t = w, w + 4, ... (a register tile of 8 tokens against four value rows at a time)
+    // ---- o_t for this warp's tokens t = w, w + warps, ... (a register tile of tokens against four value rows at a time)
     {
       float acc[kChunk / kChunkWarps];
 #pragma unroll
@@ -314,8 +317,7 @@ int run_scan(nvc_ctx* ctx, const RetArgs& a, int B, int max_qlen, void* stream) 
     if (per <= 8) ce = launch_chunk<8, VAR>(ctx, a, grid, smem, nvc_stream(stream));
     else if (per <= 16) ce = launch_chunk<16, VAR>(ctx, a, grid, smem, nvc_stream(stream));
     else if (per <= 32) ce = launch_chunk<32, VAR>(ctx, a, grid, smem, nvc_stream(stream));
-    else if (per <= 64) ce = launch_chunk<64, VAR>(ctx, a, grid, smem, nvc_stream(stream));
-    else ce = launch_chunk<128, VAR>(ctx, a, grid, smem, nvc_stream(stream));
+    else ce = launch_chunk<64, VAR>(ctx, a, grid, smem, nvc_stream(stream));      // dim <= 512: at most 64 rows per warp
     NVC_CUDA_CHECK(ctx, ce);
     ctx->launches++;
     return NVC_OK;
