@@ -138,7 +138,7 @@ __host__ __device__ inline int chunk_q_stride4(int dim) { const int q4 = (dim + 
 // The variant with per-token decays at up to 16 rows per warp is capped at 85 registers (a few spilled words) so that three CTAs -
 // what shared memory allows - fit an SM; the fixed-decay variant needs 80 as it is.
 template <int DPT, bool VAR>
-__global__ void __launch_bounds__(kChunkWarps * 32, (VAR && DPT <= 16) ? 3 : 1) retention_chunk_kernel(const RetArgs a) {
+__global__ void __launch_bounds__(kChunkWarps * 32, (VAR && DPT <= 16) ? 3 : 0) retention_chunk_kernel(const RetArgs a) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;

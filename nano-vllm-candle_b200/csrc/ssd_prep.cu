@@ -30,23 +30,44 @@ __device__ __forceinline__ int ssd_find_seq(const int32_t* cu, int B, int row) {
 
 __device__ __forceinline__ float softplus_f32(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
-// thread = (token, channel); channels are the fast index, so a warp reads neighbouring columns of a projection row
-__global__ void ssd_prep_kernel(const SsdArgs a) {
+constexpr int kPrepThreads = 256;
+
+// CTA = (token, block of 256 channels): the token's sequence is looked up once, and the step sizes of the heads whose channels the
+// CTA holds are computed once (a softplus per channel would cost more than the convolution); a warp reads neighbouring columns of a
+// projection row
+__global__ void __launch_bounds__(kPrepThreads) ssd_prep_kernel(const SsdArgs a) {
+  __shared__ int s_r0, s_fresh, s_slot;
+  __shared__ float s_dt[kPrepThreads];
   pdl_trigger();
   pdl_wait();
   const nvc_ssd_prep& p = a.p;
   const int inner = p.heads * p.vdim, gn = p.groups * p.state, C = inner + 2 * gn;
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (int64_t)a.N * C) return;
-  const int n = (int)(i / C), c = (int)(i % C);
-  int b = n, r0 = n;
-  if (p.cu_seqlens) {
-    b = ssd_find_seq(p.cu_seqlens, p.B, n);
-    r0 = p.cu_seqlens[b];
+  const int n = blockIdx.x, c0 = blockIdx.y * kPrepThreads, c = c0 + threadIdx.x;
+  if (threadIdx.x == 0) {
+    int b = n, r0 = n;
+    if (p.cu_seqlens) {
+      b = ssd_find_seq(p.cu_seqlens, p.B, n);
+      r0 = p.cu_seqlens[b];
+    }
+    s_r0 = r0;
+    s_fresh = p.positions[r0] == 0;
+    s_slot = p.state_slots[b];
   }
+  const int h_first = c0 / p.vdim;                       // the first head with channels in this CTA
+  if (c0 < inner) {
+    const int h = h_first + threadIdx.x;
+    if (h < p.heads && h * p.vdim < c0 + kPrepThreads) {
+      const float dt = softplus_f32(p.in[(int64_t)n * p.ldi + p.dt_off + h] + __ldg(p.dt_bias + h));
+      s_dt[threadIdx.x] = dt;
+      if (h * p.vdim >= c0) p.log_decay[(int64_t)n * p.ldl + h] = -expf(__ldg(p.A_log + h)) * dt;     // the CTA with the head's first channel
+    }
+  }
+  __syncthreads();
+  if (c >= C) return;
+  const int r0 = s_r0;
   const int t = n - r0;                                  // index inside the portion
-  const bool fresh = p.positions[r0] == 0;
-  const float* st = p.conv_state + (int64_t)p.state_slots[b] * (p.taps - 1) * C;
+  const bool fresh = s_fresh != 0;
+  const float* st = p.conv_state + (int64_t)s_slot * (p.taps - 1) * C;
   float acc = __ldg(p.conv_b + c);
   for (int i2 = 0; i2 < p.taps; ++i2) {
     const int idx = t - (p.taps - 1) + i2;               // the input's index inside the portion; negative: in front of it
@@ -57,11 +78,9 @@ __global__ void ssd_prep_kernel(const SsdArgs a) {
   }
   const float y = acc * sigmoid_f32(acc);
   if (c < inner) {
-    const int h = c / p.vdim;
-    const float dt = softplus_f32(p.in[(int64_t)n * p.ldi + p.dt_off + h] + __ldg(p.dt_bias + h));
+    const float dt = s_dt[c / p.vdim - h_first];
     p.x_out[(int64_t)n * p.ldx + c] = y;
     p.v_out[(int64_t)n * p.ldx + c] = dt * y;
-    if (c == h * p.vdim) p.log_decay[(int64_t)n * p.ldl + h] = -expf(__ldg(p.A_log + h)) * dt;
   } else if (c < inner + gn) {
     p.b_out[(int64_t)n * p.ldbc + c - inner] = y;
   } else {
@@ -116,8 +135,9 @@ extern "C" int nvc_ssd_prep_run(nvc_ctx* ctx, const nvc_ssd_prep* p, int N, void
   NVC_REQUIRE(ctx, N >= p->B && p->ldx >= p->heads * p->vdim && p->ldbc >= p->groups * p->state && p->ldl >= p->heads, NVC_EINVAL, "bad strides");
   const int C = p->heads * p->vdim + 2 * p->groups * p->state;
   SsdArgs a{*p, N};
-  const int64_t total = (int64_t)N * C;
-  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, ssd_prep_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, nvc_stream(stream), a));
+  if (N == 0) return NVC_OK;
+  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, ssd_prep_kernel, dim3((unsigned)N, (unsigned)((C + kPrepThreads - 1) / kPrepThreads)), dim3(kPrepThreads), 0,
+                                 nvc_stream(stream), a));
   ctx->launches++;
   return NVC_OK;
 }
