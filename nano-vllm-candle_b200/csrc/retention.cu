@@ -138,7 +138,7 @@ __host__ __device__ inline int chunk_q_stride4(int dim) { const int q4 = (dim + 
 // The variant with per-token decays at up to 16 rows per warp is capped at 85 registers (a few spilled words) so that three CTAs -
 // what shared memory allows - fit an SM; the fixed-decay variant needs 80 as it is.
 template <int DPT, bool VAR>
-__global__ void __launch_bounds__(kChunkWarps * 32, (VAR && DPT <= 16) ? 3 : 0) retention_chunk_kernel(const RetArgs a) {
+__global__ void __launch_bounds__(kChunkWarps * 32, DPT <= 16 ? 3 : 0) retention_chunk_kernel(const RetArgs a) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
@@ -170,14 +170,28 @@ __global__ void __launch_bounds__(kChunkWarps * 32, (VAR && DPT <= 16) ? 3 : 0) 
   for (int i = 0; i < DPT; ++i) S[i] = (!fresh && vok && d0 + i < dim) ? sp[(int64_t)(d0 + i) * a.vdim + v] : 0.f;
   float* q_sf = reinterpret_cast<float*>(q_s);
   float* k_sf = reinterpret_cast<float*>(k_s);
+  const bool vec = (dim & 3) == 0 && (a.ldq & 3) == 0 && (a.ldk & 3) == 0 && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k)) & 15) == 0;
   for (int c0 = r0; c0 < r1; c0 += kChunk) {
     const int n = min(kChunk, r1 - c0);
     __syncthreads();                                   // the previous chunk is done with the staged rows
-    for (int idx = threadIdx.x; idx < kChunk * dim4; idx += blockDim.x) {
-      const int t = idx / dim4, d = idx - t * dim4;
-      const bool in = t < n && d < dim;
-      q_sf[t * 4 * RS + d] = in ? a.q[(int64_t)(c0 + t) * a.ldq + hq * dim + d] : 0.f;
-      k_sf[t * dim4 + d] = in ? a.k[(int64_t)(c0 + t) * a.ldk + hq * dim + d] : 0.f;
+    // a warp stages whole rows (t = w, w + warps, ...), lanes along the row: no index division, 16-byte loads where the layout allows
+    for (int t = w; t < kChunk; t += kChunkWarps) {
+      const bool tin = t < n;
+      const float* qrow = a.q + (int64_t)(c0 + t) * a.ldq + hq * dim;
+      const float* krow = a.k + (int64_t)(c0 + t) * a.ldk + hq * dim;
+      if (vec) {
+        for (int d4 = lane; d4 < q4; d4 += 32) {
+          const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+          q_s[t * RS + d4] = tin ? *reinterpret_cast<const float4*>(qrow + 4 * d4) : z;
+          k_s[t * q4 + d4] = tin ? *reinterpret_cast<const float4*>(krow + 4 * d4) : z;
+        }
+      } else {
+        for (int d = lane; d < dim4; d += 32) {
+          const bool in = tin && d < dim;
+          q_sf[t * 4 * RS + d] = in ? qrow[d] : 0.f;
+          k_sf[t * dim4 + d] = in ? krow[d] : 0.f;
+        }
+      }
     }
     if (VAR && threadIdx.x < 32) {        // inclusive running sums of the chunk's log decays (a fixed order: lane by lane)
       float l = lane < n ? a.log_decay[(int64_t)(c0 + lane) * a.ldl + h] : 0.f;
