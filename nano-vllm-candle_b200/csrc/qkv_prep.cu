@@ -9,7 +9,8 @@
 //   value blending                           v <- (1 - lambda) v + lambda v_first, or v_first <- v in the layer that provides it
 //   v *= v_scale                             (a constant weight of the mixer, so that every attention kernel can leave it out)
 //   stores                                   q to its buffer; k and v to rows of a paged cache (slot mapping) or to plain rows
-// One warp per (token, head) of q, k or v; a head is staged in shared memory so that any pairing reads its partner.
+// One warp per (token, head) of q, k or v; a head is staged in shared memory so that any pairing reads its partner.  The purely
+// element-wise case (bias and silu only, plain fp32 rows out) runs a flat kernel with 16-byte accesses instead.
 #include "typed.cuh"
 
 namespace {
@@ -89,6 +90,30 @@ __global__ void qkv_prep_kernel(const PrepArgs a) {
 }
 
 
+// The element-wise case (no norm, no rotation, no blending, no scale, plain fp32 rows out): q, k, v = act(in + bias), four numbers per
+// thread.  CTA = (token, block of 256 x 4 columns of [q | k | v]).
+__global__ void __launch_bounds__(256) prep_flat_kernel(const PrepArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const nvc_qkv_prep& p = a.p;
+  const int qw = p.q_heads * p.dim, kw = p.kv_heads * p.dim, vw = p.kv_heads * p.vdim;
+  const int64_t n = blockIdx.x;
+  const int j = 4 * (blockIdx.y * blockDim.x + threadIdx.x);          // column of [q | k | v]
+  if (j >= qw + kw + vw) return;
+  int col;
+  float* out;
+  if (j < qw) { col = p.q_off + j; out = reinterpret_cast<float*>(p.q_out) + n * p.ldq + j; }
+  else if (j < qw + kw) { col = p.k_off + j - qw; out = reinterpret_cast<float*>(p.k_out) + n * p.ldk + j - qw; }
+  else { col = p.v_off + j - qw - kw; out = reinterpret_cast<float*>(p.v_out) + n * p.ldv + j - qw - kw; }
+  float4 v = *reinterpret_cast<const float4*>(p.in + n * p.ldi + col);
+  if (p.bias) {
+    const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+  }
+  if (p.act == NVC_PREP_ACT_SILU) { v.x *= sigmoid_f32(v.x); v.y *= sigmoid_f32(v.y); v.z *= sigmoid_f32(v.z); v.w *= sigmoid_f32(v.w); }
+  *reinterpret_cast<float4*>(out) = v;
+}
+
 // one warp per (token, head) of a query projection laid out [heads][dim | rot_dim]: the unrotated part goes to out_a, the rotated
 // part (turned by the token's position) to out_b
 template <typename T>
@@ -148,6 +173,21 @@ extern "C" int nvc_qkv_prep_run(nvc_ctx* ctx, const nvc_qkv_prep* p, int N, void
   NVC_REQUIRE(ctx, p->ldq >= p->q_heads * p->dim && p->ldk >= p->kv_heads * p->dim && p->ldv >= p->kv_heads * p->vdim, NVC_EINVAL,
               "bad strides");
   if (N == 0) return NVC_OK;
+  {
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    const int qw = p->q_heads * p->dim, kw = p->kv_heads * p->dim, vw = p->kv_heads * p->vdim;
+    const bool flat = p->q_dtype == NVC_DT_F32 && p->kv_dtype == NVC_DT_F32 && !p->q_norm && !p->unit_norm && p->rot_dims == 0 &&
+                      p->blend == NVC_BLEND_NONE && !p->slot_mapping && p->k_scale == 1.f && p->v_scale == 1.f &&
+                      ((qw | kw | vw | p->q_off | p->k_off | p->v_off | p->ldi | p->ldq | p->ldk | p->ldv) & 3) == 0 && al16(p->in) &&
+                      al16(p->bias) && al16(p->q_out) && al16(p->k_out) && al16(p->v_out);
+    if (flat) {
+      PrepArgs a{*p, N};
+      NVC_CUDA_CHECK(ctx, nvc_launch(ctx, prep_flat_kernel, dim3((unsigned)N, (unsigned)(((qw + kw + vw) / 4 + 255) / 256)), dim3(256), 0,
+                                     nvc_stream(stream), a));
+      ctx->launches++;
+      return NVC_OK;
+    }
+  }
   if (p->q_dtype == NVC_DT_F32 && p->kv_dtype == NVC_DT_F32) return launch_prep<float, float>(ctx, p, N, stream);
   if (p->q_dtype == NVC_DT_BF16 && p->kv_dtype == NVC_DT_BF16) return launch_prep<__nv_bfloat16, __nv_bfloat16>(ctx, p, N, stream);
   if (p->q_dtype == NVC_DT_BF16 && p->kv_dtype == NVC_DT_F32) return launch_prep<__nv_bfloat16, float>(ctx, p, N, stream);

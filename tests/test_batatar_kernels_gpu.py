@@ -115,10 +115,12 @@ def test_bias_then_heads_divided_by_their_root_mean_square(ctx, ops, dt, H, G, d
     assert float(kc[untouched].abs().max()) == 0.0
 
 
-def test_silu_on_all_three_projections(ctx, ops):
+@pytest.mark.parametrize("H,d,vd,pad", [(3, 16, 24, 8), (3, 5, 7, 1), (16, 128, 128, 0)])
+def test_silu_on_all_three_projections(ctx, ops, H, d, vd, pad):
+    """Sizes whose rows allow 16-byte accesses take the flat element-wise kernel, the others the general one."""
     g = gen(5)
-    N, H, d, vd = 6, 3, 16, 24
-    x = torch.randn(N, 2 * H * d + H * vd + 8, generator=g) * 2
+    N = 6
+    x = torch.randn(N, 2 * H * d + H * vd + pad, generator=g) * 2
     q, k, v = (torch.empty(N, H * w, device=DEV) for w in (d, d, vd))
     ops.qkv_prep(ctx, x.to(DEV), 0, H * d, 2 * H * d, H, H, d, vd, q, k, v, silu=True)
     assert torch.allclose(q.cpu(), B.silu(x[:, :H * d]), rtol=2e-5, atol=2e-5)
