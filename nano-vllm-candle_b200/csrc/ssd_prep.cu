@@ -32,17 +32,20 @@ __device__ __forceinline__ float softplus_f32(float x) { return fmaxf(x, 0.f) + 
 
 constexpr int kPrepThreads = 256;
 
-// CTA = (token, block of 256 channels): the token's sequence is looked up once, and the step sizes of the heads whose channels the
-// CTA holds are computed once (a softplus per channel would cost more than the convolution); a warp reads neighbouring columns of a
-// projection row
+// CTA = (token, block of 256 x CW channels): the token's sequence is looked up once, and the step sizes of the heads whose channels
+// the CTA holds are computed once (a softplus per channel would cost more than the convolution).  A thread takes CW neighbouring
+// channels - 4 with 16-byte accesses when every width, offset and stride is a multiple of 4 (a head never ends inside a thread's
+// four), else 1 - and a warp reads neighbouring columns of a projection row.
+template <int CW>
 __global__ void __launch_bounds__(kPrepThreads) ssd_prep_kernel(const SsdArgs a) {
+  constexpr int kSpan = kPrepThreads * CW;
   __shared__ int s_r0, s_fresh, s_slot;
-  __shared__ float s_dt[kPrepThreads];
+  __shared__ float s_dt[kSpan];
   pdl_trigger();
   pdl_wait();
   const nvc_ssd_prep& p = a.p;
   const int inner = p.heads * p.vdim, gn = p.groups * p.state, C = inner + 2 * gn;
-  const int n = blockIdx.x, c0 = blockIdx.y * kPrepThreads, c = c0 + threadIdx.x;
+  const int n = blockIdx.x, c0 = blockIdx.y * kSpan, c = c0 + CW * threadIdx.x;
   if (threadIdx.x == 0) {
     int b = n, r0 = n;
     if (p.cu_seqlens) {
@@ -55,10 +58,9 @@ __global__ void __launch_bounds__(kPrepThreads) ssd_prep_kernel(const SsdArgs a)
   }
   const int h_first = c0 / p.vdim;                       // the first head with channels in this CTA
   if (c0 < inner) {
-    const int h = h_first + threadIdx.x;
-    if (h < p.heads && h * p.vdim < c0 + kPrepThreads) {
+    for (int h = h_first + threadIdx.x; h < p.heads && h * p.vdim < c0 + kSpan; h += kPrepThreads) {
       const float dt = softplus_f32(p.in[(int64_t)n * p.ldi + p.dt_off + h] + __ldg(p.dt_bias + h));
-      s_dt[threadIdx.x] = dt;
+      s_dt[h - h_first] = dt;
       if (h * p.vdim >= c0) p.log_decay[(int64_t)n * p.ldl + h] = -expf(__ldg(p.A_log + h)) * dt;     // the CTA with the head's first channel
     }
   }
@@ -68,24 +70,43 @@ __global__ void __launch_bounds__(kPrepThreads) ssd_prep_kernel(const SsdArgs a)
   const int t = n - r0;                                  // index inside the portion
   const bool fresh = s_fresh != 0;
   const float* st = p.conv_state + (int64_t)s_slot * (p.taps - 1) * C;
-  float acc = __ldg(p.conv_b + c);
+  float acc[CW], y[CW];
+  if (CW == 4) {
+    const float4 b4 = *reinterpret_cast<const float4*>(p.conv_b + c);
+    acc[0] = b4.x; acc[1 % CW] = b4.y; acc[2 % CW] = b4.z; acc[3 % CW] = b4.w;
+  } else {
+    acc[0] = __ldg(p.conv_b + c);
+  }
   for (int i2 = 0; i2 < p.taps; ++i2) {
     const int idx = t - (p.taps - 1) + i2;               // the input's index inside the portion; negative: in front of it
-    float x;
-    if (idx >= 0) x = p.in[(int64_t)(r0 + idx) * p.ldi + p.xbc_off + c];
-    else x = fresh ? 0.f : st[(int64_t)(p.taps - 1 + idx) * C + c];
-    acc = fmaf(__ldg(p.conv_w + (int64_t)i2 * C + c), x, acc);
+    const float* xp = idx >= 0 ? p.in + (int64_t)(r0 + idx) * p.ldi + p.xbc_off + c : st + (int64_t)(p.taps - 1 + idx) * C + c;
+    const float* wp = p.conv_w + (int64_t)i2 * C + c;
+    const bool zero = idx < 0 && fresh;
+    if (CW == 4) {
+      const float4 x4 = zero ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(xp);
+      const float4 w4 = *reinterpret_cast<const float4*>(wp);
+      acc[0] = fmaf(w4.x, x4.x, acc[0]); acc[1 % CW] = fmaf(w4.y, x4.y, acc[1 % CW]);
+      acc[2 % CW] = fmaf(w4.z, x4.z, acc[2 % CW]); acc[3 % CW] = fmaf(w4.w, x4.w, acc[3 % CW]);
+    } else {
+      acc[0] = fmaf(__ldg(wp), zero ? 0.f : *xp, acc[0]);
+    }
   }
-  const float y = acc * sigmoid_f32(acc);
+#pragma unroll
+  for (int u = 0; u < CW; ++u) y[u] = acc[u] * sigmoid_f32(acc[u]);
+  float* out;
   if (c < inner) {
     const float dt = s_dt[c / p.vdim - h_first];
-    p.x_out[(int64_t)n * p.ldx + c] = y;
-    p.v_out[(int64_t)n * p.ldx + c] = dt * y;
+    out = p.x_out + (int64_t)n * p.ldx + c;
+    float* vo = p.v_out + (int64_t)n * p.ldx + c;
+    if (CW == 4) *reinterpret_cast<float4*>(vo) = make_float4(dt * y[0], dt * y[1 % CW], dt * y[2 % CW], dt * y[3 % CW]);
+    else vo[0] = dt * y[0];
   } else if (c < inner + gn) {
-    p.b_out[(int64_t)n * p.ldbc + c - inner] = y;
+    out = p.b_out + (int64_t)n * p.ldbc + c - inner;
   } else {
-    p.c_out[(int64_t)n * p.ldbc + c - inner - gn] = y;
+    out = p.c_out + (int64_t)n * p.ldbc + c - inner - gn;
   }
+  if (CW == 4) *reinterpret_cast<float4*>(out) = make_float4(y[0], y[1 % CW], y[2 % CW], y[3 % CW]);
+  else out[0] = y[0];
 }
 
 // thread = (sequence, channel): reads the taps - 1 inputs that end the sequence so far, then writes them
@@ -136,8 +157,17 @@ extern "C" int nvc_ssd_prep_run(nvc_ctx* ctx, const nvc_ssd_prep* p, int N, void
   const int C = p->heads * p->vdim + 2 * p->groups * p->state;
   SsdArgs a{*p, N};
   if (N == 0) return NVC_OK;
-  NVC_CUDA_CHECK(ctx, nvc_launch(ctx, ssd_prep_kernel, dim3((unsigned)N, (unsigned)((C + kPrepThreads - 1) / kPrepThreads)), dim3(kPrepThreads), 0,
-                                 nvc_stream(stream), a));
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const int gn = p->groups * p->state;
+  const bool vec = ((p->vdim | gn | p->ldi | p->xbc_off | p->ldx | p->ldbc) & 3) == 0 && al16(p->in) && al16(p->conv_w) && al16(p->conv_b) &&
+                   al16(p->conv_state) && al16(p->x_out) && al16(p->v_out) && al16(p->b_out) && al16(p->c_out);
+  if (vec) {
+    NVC_CUDA_CHECK(ctx, nvc_launch(ctx, ssd_prep_kernel<4>, dim3((unsigned)N, (unsigned)((C + 4 * kPrepThreads - 1) / (4 * kPrepThreads))),
+                                   dim3(kPrepThreads), 0, nvc_stream(stream), a));
+  } else {
+    NVC_CUDA_CHECK(ctx, nvc_launch(ctx, ssd_prep_kernel<1>, dim3((unsigned)N, (unsigned)((C + kPrepThreads - 1) / kPrepThreads)), dim3(kPrepThreads), 0,
+                                   nvc_stream(stream), a));
+  }
   ctx->launches++;
   return NVC_OK;
 }

@@ -296,7 +296,7 @@ def test_state_space_layer_carries_both_states_between_portions_and_slots(ctx, o
     portions down to one and two tokens (shorter than the taps), in slots that an earlier owner left full."""
     g = gen(20)
     inner, C = H * vd, H * vd + 2 * G * N
-    pad = 6
+    pad = 8 if H % 4 == 0 else 6          # rows that allow 16-byte accesses (first and fourth case) and rows that do not
     ld = pad + inner + C + H            # [pad | z | x B C | dt]
     conv_w, conv_b = torch.randn(C, taps, generator=g) * taps ** -0.5, torch.randn(C, generator=g) * 0.2
     A_log, dt_bias, D = torch.log(0.1 + 1.5 * torch.rand(H, generator=g)), torch.randn(H, generator=g) * 0.5, torch.randn(H, generator=g)
