@@ -33,7 +33,7 @@ def gen(seed):
 
 # ------------------------------------------------------------------------------------------ residual sums and norms
 @pytest.mark.parametrize("dt", DTS)
-@pytest.mark.parametrize("H", [24, 37, 192, 1100, 5000])
+@pytest.mark.parametrize("H", [24, 37, 208, 1100, 5000])
 def test_sum_of_two_normed_branches_and_the_next_norm(ctx, ops, dt, H):
     g = gen(2)
     N, eps = 7, 1e-3
@@ -94,7 +94,7 @@ def test_gate_in_front_of_or_behind_a_norm_in_groups(ctx, ops, dt, groups, gsize
 
 # ------------------------------------------------------------------------------------------ projections' epilogue: bias, unit heads, silu
 @pytest.mark.parametrize("dt", DTS)
-@pytest.mark.parametrize("H,G,d,vd", [(4, 2, 16, 24), (3, 3, 40, 8), (8, 1, 48, 80), (2, 2, 128, 64)])
+@pytest.mark.parametrize("H,G,d,vd", [(4, 2, 16, 24), (3, 3, 40, 8), (8, 1, 24, 80), (2, 2, 128, 64)])
 def test_bias_then_heads_divided_by_their_root_mean_square(ctx, ops, dt, H, G, d, vd):
     g = gen(4)
     N, eps, pad = 9, 1e-3, 5
@@ -179,7 +179,7 @@ def run_chunk_attention(ctx, ops, dt, H, G, d, vd, lens, qlens, bs, chunk, cap, 
     return got.float().cpu(), torch.cat(want), vs[0]
 
 
-SHAPES = [(4, 2, 32, 48), (3, 3, 40, 24), (6, 1, 16, 80), (2, 2, 64, 128), (8, 4, 48, 80)]
+SHAPES = [(4, 2, 32, 48), (3, 3, 40, 24), (6, 1, 16, 80), (2, 2, 64, 128), (8, 2, 48, 96)]
 
 
 @pytest.mark.parametrize("dt", DTS)
@@ -290,7 +290,7 @@ SLOTS = {"a": 2, "b": 0, "c": 3}
 
 
 @pytest.mark.parametrize("form", ["token by token", "32 tokens at a time"])
-@pytest.mark.parametrize("H,G,N,vd,taps", [(4, 2, 8, 16, 4), (3, 3, 16, 24, 2), (2, 1, 32, 64, 3), (8, 2, 32, 32, 4), (1, 1, 128, 40, 1), (6, 1, 5, 7, 5)])
+@pytest.mark.parametrize("H,G,N,vd,taps", [(4, 2, 8, 16, 4), (3, 3, 16, 24, 2), (2, 1, 32, 64, 3), (8, 4, 24, 32, 3), (1, 1, 128, 40, 1), (6, 1, 5, 7, 5)])
 def test_state_space_layer_carries_both_states_between_portions_and_slots(ctx, ops, H, G, N, vd, taps, form):
     """Convolution with bias and silu, step sizes, the recurrence and the skip term against the token-by-token restatement, over
     portions down to one and two tokens (shorter than the taps), in slots that an earlier owner left full."""
@@ -369,7 +369,7 @@ def test_a_decay_that_underflows_inside_a_chunk(ctx, ops):
 
 # ------------------------------------------------------------------------------------------ lightning attention
 @pytest.mark.parametrize("form", ["token by token", "32 tokens at a time"])
-@pytest.mark.parametrize("H,d,vd", [(3, 16, 24), (4, 64, 64), (1, 8, 1), (2, 200, 72)])
+@pytest.mark.parametrize("H,d,vd", [(3, 16, 24), (4, 64, 48), (1, 8, 1), (2, 200, 72)])
 def test_constant_decay_recurrence_between_portions_and_slots(ctx, ops, H, d, vd, form):
     g = gen(22)
     decay = torch.tensor([0.5, 0.999, 0.97, 0.0])[:H].contiguous()

@@ -47,8 +47,8 @@ def cfg_b(all_experts=False):
 def cfg_c(all_experts=False):
     """Sizes of the tensor-pipe routes of the bf16 mode: heads of 64 and 128 numbers, experts of 128 hidden units (grouped tcgen05
     products), a loop over the whole model."""
-    return B.make_config(vocab=160, width=128, residual_mult=0.3, loop=(0, 2, 2), layers=[
-        B.with_moe(B.parallel_cfg(heads=4, kv_heads=2, dim=64, vdim=64, chunk=48, scale=0.1, softcap=20.0, s_heads=4, s_vdim=32, s_state=32,
+    return B.make_config(vocab=160, width=128, residual_mult=0.35, loop=(0, 2, 2), layers=[
+        B.with_moe(B.parallel_cfg(heads=4, kv_heads=2, dim=64, vdim=64, chunk=48, scale=0.1, softcap=25.0, s_heads=4, s_vdim=32, s_state=32,
                                   s_groups=2, conv=4, norm_groups=2), 4, 4 if all_experts else 2, 128),
         B.with_moe(B.lightning_cfg(heads=2, dim=64, vdim=128), 3, 3 if all_experts else 1, 160),
     ])
